@@ -56,9 +56,24 @@ CORE = {
     "sb_attn_prep": ("i", "piiiiiiiiiiiippppifppppipipiis"),
     "sb_attn_unrotate": ("i", "ppiiiiiipps"),
     "sb_linrec_prep": ("i", "piiiiiiffiipppfppiiis"),
-    "sb_linrec_scan": ("i", "piiiippippiiipps"),
+    "sb_linrec_scan": ("i", "piiiipppiippiiipps"),
     "sb_linrec_force_columns": ("v", "i"),
-    "sb_linrec_out": ("i", "ppiiiiipifpis"),
+    "sb_linrec_out": ("i", "ppiiiiipiiifpis"),
+    "sb_embed_pair": ("i", "pippppppiipiiiifps"),
+    "sb_keep_last_token": ("i", "pppips"),
+    "sb_layernorm": ("i", "ppiipifpis"),
+    "sb_causal_conv": ("i", "piiiiippiiiipppppppiiis"),
+    "sb_delta_prep": ("i", "piiiiiiiipppiffps"),
+    "sb_delta_scan": ("i", "piiiipippiipps"),
+    "sb_ssd_prep": ("i", "piiipiiiiippips"),
+    "sb_ssd_out": ("i", "ppiiipiiiiippifpis"),
+    "sb_attention_sigmoid": ("i", "ppiippppipiiiiiiffps"),
+    "sb_moe_route": ("i", "piiipps"),
+    "sb_moe_max_tiles": ("i", "ii"),
+    "sb_moe_group": ("i", "piipps"),
+    "sb_moe_up": ("i", "pipippiiiiiffps"),
+    "sb_moe_down": ("i", "pipippiiiiips"),
+    "sb_moe_combine": ("i", "pppiiis"),
     "sb_sample_params_size": ("i", ""),
     "sb_sample": ("i", "piippipps"),
     "sb_add_i32": ("i", "piis"),

@@ -10,9 +10,12 @@ at a time; here sequences of a batch share pools of pages.
   window) and has storage of its own: `[entry, page, k|v, kv head, position in page, hd]`, one
   pool of pages, one page list per sequence (all entries of a group grow together).
 * A group with a window gives back the pages whose keys no later query can see, so a
-  sequence holds about `window` keys there, however long it grows.
+  sequence holds about `window` keys there, however long it grows (plus the pages of the first
+  `keep_first` keys, when the window keeps those in sight for good).
 * A **slot** is a sequence's record: its length, its page lists, and its row in every state
-  tensor.  Slots and pages are handed back when the sequence ends and are used again; a reused
+  tensor.  A schedule entry may ask for one state tensor or for several by name; the model as a
+  whole may ask for named ones too (`model_state`).  `state` maps an entry's index, or (entry,
+  name), or ("model", name), to a tensor [slot, ...].  Slots and pages are handed back when the sequence ends and are used again; a reused
   slot starts at length 0 with zeroed state, and stale keys in reused pages are never read
   because lengths bound every read.
 """
@@ -34,6 +37,7 @@ class KVNeed:
     n_kv_heads: int
     head_dim: int
     window: int = 0            # 0: all keys stay; n: only the last n keys are ever read
+    keep_first: int = 0        # with a window: the first n keys of a sequence are read for good too
 
 
 @dataclass(frozen=True)
@@ -74,8 +78,12 @@ class Cache:
     """All groups, the slot table and the state tensors of one engine."""
 
     def __init__(self, kv_needs: list, state_needs: list, max_tokens: int, dtype, device,
-                 n_slots: Optional[int] = None, page_size: int = PAGE_SIZE):
-        """`kv_needs[i]` / `state_needs[i]` are what schedule entry i asks for (None: nothing).
+                 n_slots: Optional[int] = None, page_size: int = PAGE_SIZE,
+                 model_state: Optional[dict] = None):
+        """`kv_needs[i]` / `state_needs[i]` are what schedule entry i asks for (None: nothing; a
+        state need is one StateNeed or a dict of them by name, the name None standing for the
+        entry's unnamed one).  `model_state`: named StateNeeds
+        that belong to no entry.
         `max_tokens` is the most tokens live sequences hold together, each sequence's count
         rounded up to a whole page."""
         if max_tokens <= 0:
@@ -93,8 +101,15 @@ class Cache:
         self.groups = [CacheGroup(need, entries, self.n_pages, page_size, dtype, device)
                        for need, entries in by_need.items()]
         self.group_of_entry = {e: gi for gi, g in enumerate(self.groups) for e in g.entries}
-        self.state = {entry: torch.zeros((self.n_slots, *need.shape), dtype=need.dtype, device=device)
-                      for entry, need in enumerate(state_needs) if need is not None}
+        wanted = {}
+        for entry, need in enumerate(state_needs):
+            if isinstance(need, dict):
+                wanted.update({(entry if name is None else (entry, name)): n for name, n in need.items()})
+            elif need is not None:
+                wanted[entry] = need
+        wanted.update({("model", name): n for name, n in (model_state or {}).items()})
+        self.state = {key: torch.zeros((self.n_slots, *need.shape), dtype=need.dtype, device=device)
+                      for key, need in wanted.items()}
 
     # ------------------------------------------------------------------ sequences
     def open(self) -> int:
@@ -166,10 +181,12 @@ class Cache:
                 continue
             # the next query sits at position >= new_len and sees keys j > position - w
             dead_pages = max(0, new_len - w + 1) // self.page_size     # pages wholly at j <= new_len - w
-            give = [pages[i] for i in range(min(dead_pages, len(pages))) if pages[i] is not None]
+            kept_pages = (g.need.keep_first + self.page_size - 1) // self.page_size   # pages with a key that stays in sight
+            dead = range(kept_pages, min(dead_pages, len(pages)))
+            give = [pages[i] for i in dead if pages[i] is not None]
             if give:
                 g.pool.give_back(give)
-                for i in range(min(dead_pages, len(pages))):
+                for i in dead:
                     pages[i] = None
 
     def truncate(self, slot: int, new_len: int) -> bool:
@@ -185,7 +202,7 @@ class Cache:
         keep = (new_len + self.page_size - 1) // self.page_size
         for g, pages in zip(self.groups, rec.pages):
             first_seen = max(0, new_len - g.need.window + 1) // self.page_size if g.need.window else 0
-            if any(p is None for p in pages[first_seen:keep]):
+            if any(p is None for p in pages[first_seen:keep]):      # (pages of kept first keys are never given back)
                 return False
         for g, pages in zip(self.groups, rec.pages):
             g.pool.give_back([p for p in pages[keep:] if p is not None])

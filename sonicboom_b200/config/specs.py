@@ -62,6 +62,27 @@ class FeedForwardSpec:
 
 
 @dataclass(frozen=True)
+class ConvSpec:
+    """A short causal convolution over time on every channel of what a sublayer reads, added to
+    it: h <- h + conv(h), conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j), zeros before a
+    sequence's start.  `tensor` is [width, taps]."""
+    tensor: str
+    width: int
+    taps: int
+
+
+@dataclass(frozen=True)
+class PairEmbeddingSpec:
+    """A second embedding table read by a hash of two neighbouring tokens and added to the token's
+    own row: row (previous * mul_prev + current * mul_cur) mod buckets, and row `buckets` (the
+    table's last) for a sequence's first token.  `tensor` is [buckets + 1, width]."""
+    tensor: str
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+
+
+@dataclass(frozen=True)
 class DepthMixSpec:
     """What goes on to the next schedule entry instead of a block's own result: a combination of
     the embedding output and every block result so far (`n_inputs` of them, this block's last)."""
@@ -83,6 +104,8 @@ class LayerSpec:
     mixer_post_norm: Optional[NormSpec] = None
     feed_forward_post_norm: Optional[NormSpec] = None
     depth_mix: Optional[DepthMixSpec] = None
+    mixer_conv: Optional[ConvSpec] = None          # on the mixer's input, after its norm
+    feed_forward_conv: Optional[ConvSpec] = None   # on the feed-forward's input, after its norm
 
     @property
     def kind(self) -> str:
@@ -125,6 +148,7 @@ class ModelSpec:
     logit_cap: float = 0.0              # c > 0: logits = c * tanh(logits / c); 0: no cap
     injections: tuple = ()              # of StreamInjection, at most one per schedule entry
     unused_tensors: tuple = ()          # (name, shape) of tensors a file may hold that nothing reads
+    pair_embedding: Optional[PairEmbeddingSpec] = None   # added to every embedding row
 
     def validate(self) -> None:
         if not self.layers:

@@ -4,8 +4,10 @@
 //
 // per head, token by token in float32, for prompts, portions and single tokens alike: every token
 // is the same arithmetic whatever the step brings, so a result does not depend on how a sequence
-// was cut or on what else the step holds.  The decay is either one value per (token, head, key
-// channel) read from a tensor, or one fixed value per head.
+// was cut or on what else the step holds.  The decay is one value per (token, head, key channel)
+// read from a tensor, one fixed value per head, or one value per (token, head) read from a tensor.
+// Several heads may share one q and k (`heads_per_qk` neighbouring heads read the same ones), as
+// the heads of a state-space layer share its input and output maps.
 //
 // A column of S (the `dim` values that belong to one value channel) is shared by 16 lanes that
 // keep their runs of it in registers for the whole step (of one column, or of two neighbouring
@@ -46,24 +48,28 @@ struct Runs {
 // STAGES groups of tokens in shared memory: one in use, the others on their way.
 // CPT columns per thread: a lane keeps its runs of CPT neighbouring columns, so that what it reads of
 // a token's q, k and decays serves CPT columns.
-template <int NPL, bool PER_CHANNEL, bool VEC, int STAGES, int CPT>
+template <int NPL, int MODE, bool VEC, int STAGES, int CPT>
 __global__ void __launch_bounds__(THREADS)
 linrec_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, const float* decay,
-                   const float* __restrict__ head_decay, const int32_t* seq_row0, const int32_t* seq_slot,
+                   const float* __restrict__ head_decay, const float* token_decay, int heads_per_qk,
+                   const int32_t* seq_row0, const int32_t* seq_slot,
                    int n_heads, int dim, int vdim, float* state, float* out) {
   extern __shared__ __align__(16) float smem[];
+  constexpr bool PER_CHANNEL = MODE == 1;               // a decay per key channel
+  constexpr bool PER_TOKEN = MODE == 2;                 // a decay per token and head
   constexpr int PAD = NPL * LANES;                      // channels with padding
   constexpr int NARR = PER_CHANNEL ? 3 : 2;             // q, k (, decay)
   constexpr int R = Runs<NPL>::R;
   constexpr int COLS = GROUPS * CPT;                   // columns of a block
-  constexpr int ROW = NARR * PAD + COLS;                // floats of a staged token
+  constexpr int ROW = NARR * PAD + COLS + (PER_TOKEN ? 4 : 0);   // floats of a staged token
   sb_pdl_launch();
   const int b = blockIdx.z, h = blockIdx.y;
   const int tid = threadIdx.x, sub = tid % LANES, cl = tid / LANES;
   const int col0 = blockIdx.x * COLS, col = col0 + cl * CPT;      // this thread's first column
   const int row0 = seq_row0[b], n = seq_row0[b + 1] - row0;
   const int slot = seq_slot[b];
-  const float a_head = PER_CHANNEL ? 1.0f : head_decay[h];
+  const float a_head = MODE == 0 ? head_decay[h] : 1.0f;
+  const int hq = h / heads_per_qk;                      // the q and k this head reads
   // padding channels and columns stay zero for good: cp.async writes the others only
   if (dim < PAD || vdim - col0 < COLS) {
     for (int i = tid; i < STAGES * TB * ROW; i += THREADS) smem[i] = 0.0f;
@@ -86,7 +92,7 @@ linrec_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, c
   // (VEC) or one value of q, k, the decays or the block's values; `src[k]` points into the
   // sequence's first row, `step[k]` is that tensor's row stride.
   constexpr int V = VEC ? 4 : 1;
-  constexpr int PIECES = NARR * PAD / V + COLS / V;     // at most, per token
+  constexpr int PIECES = NARR * PAD / V + COLS / V + (PER_TOKEN ? 1 : 0);     // at most, per token
   constexpr int MINE = (PIECES + THREADS - 1) / THREADS;
   const float* src[MINE];
   int dst[MINE], step[MINE], width[MINE];               // width: values of the piece (0: none)
@@ -99,8 +105,8 @@ linrec_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, c
       src[k] = proj, dst[k] = 0, step[k] = 0, width[k] = 0;
       if (arr < NARR) {
         const int c = (e - arr * per_arr) * V;
-        src[k] = arr == 0 ? proj + (size_t)row0 * ld + q_off + h * dim + c
-               : arr == 1 ? proj + (size_t)row0 * ld + k_off + h * dim + c
+        src[k] = arr == 0 ? proj + (size_t)row0 * ld + q_off + hq * dim + c
+               : arr == 1 ? proj + (size_t)row0 * ld + k_off + hq * dim + c
                           : decay + (size_t)row0 * per_row + (size_t)h * dim + c;
         step[k] = arr == 2 ? (int)per_row : ld;
         dst[k] = arr * PAD + c;
@@ -111,6 +117,11 @@ linrec_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, c
         step[k] = ld;
         dst[k] = NARR * PAD + c;
         width[k] = min(V, n_cols - c);
+      } else if (PER_TOKEN && e - NARR * per_arr == n_vals) {
+        src[k] = token_decay + (size_t)row0 * n_heads + h;
+        step[k] = n_heads;
+        dst[k] = NARR * PAD + COLS;
+        width[k] = 1;
       }
     }
   }
@@ -157,6 +168,7 @@ linrec_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, c
         float v[CPT];
 #pragma unroll
         for (int x = 0; x < CPT; ++x) v[x] = tok[NARR * PAD + cl * CPT + x];
+        const float a_tok = PER_TOKEN ? tok[NARR * PAD + COLS] : a_head;
 #pragma unroll
         for (int j = 0; j < NPL / R; ++j) {
           float qv[R], kv[R], av[R];
@@ -177,7 +189,7 @@ linrec_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, c
           for (int x = 0; x < CPT; ++x)
 #pragma unroll
             for (int u = 0; u < R; ++u) {
-              const float sv = fmaf(PER_CHANNEL ? av[u] : a_head, S[x][j * R + u], kv[u] * v[x]);
+              const float sv = fmaf(PER_CHANNEL ? av[u] : a_tok, S[x][j * R + u], kv[u] * v[x]);
               S[x][j * R + u] = sv;
               acc[x][tt] = fmaf(sv, qv[u], acc[x][tt]);
             }
@@ -214,8 +226,8 @@ linrec_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, c
 }
 
 template <int NPL>
-constexpr size_t scan_smem(bool per_channel, int stages, int cpt) {
-  return (size_t)stages * TB * ((per_channel ? 3 : 2) * NPL * LANES + GROUPS * cpt) * sizeof(float);
+constexpr size_t scan_smem(int mode, int stages, int cpt) {
+  return (size_t)stages * TB * ((mode == 1 ? 3 : 2) * NPL * LANES + GROUPS * cpt + (mode == 2 ? 4 : 0)) * sizeof(float);
 }
 
 int sm_count() {
@@ -234,9 +246,9 @@ long fits(size_t smem) {
   return (long)sm_count() * (per_sm < 16 ? per_sm : 16);
 }
 
-template <int NPL, bool PC, bool VEC, int STAGES, int CPT>
+template <int NPL, int PC, bool VEC, int STAGES, int CPT>
 cudaError_t launch_scan(dim3 grid, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off, int v_off,
-                        const float* decay, const float* head_decay, const int32_t* seq_row0,
+                        const float* decay, const float* head_decay, const float* token_decay, int heads_per_qk, const int32_t* seq_row0,
                         const int32_t* seq_slot, int n_heads, int dim, int vdim, float* state, float* out) {
   constexpr size_t smem = scan_smem<NPL>(PC, STAGES, CPT);
   static bool configured = false;
@@ -247,25 +259,25 @@ cudaError_t launch_scan(dim3 grid, cudaStream_t stream, const float* proj, int l
   }
   configured = true;
   return sb_launch<SB_K_OTHER>(linrec_scan_kernel<NPL, PC, VEC, STAGES, CPT>, grid, dim3(THREADS), smem, stream, proj, ld,
-                               q_off, k_off, v_off, decay, head_decay, seq_row0, seq_slot, n_heads, dim, vdim, state, out);
+                               q_off, k_off, v_off, decay, head_decay, token_decay, heads_per_qk, seq_row0, seq_slot, n_heads, dim, vdim, state, out);
 }
 
 // Three stages, unless the grid then needs a second wave of blocks that two stages spare it.
-template <int NPL, bool PC, bool VEC, int CPT>
+template <int NPL, int PC, bool VEC, int CPT>
 cudaError_t launch_scan_staged(int n_seqs, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off,
-                               int v_off, const float* decay, const float* head_decay, const int32_t* seq_row0,
+                               int v_off, const float* decay, const float* head_decay, const float* token_decay, int heads_per_qk, const int32_t* seq_row0,
                                const int32_t* seq_slot, int n_heads, int dim, int vdim, float* state, float* out) {
   const dim3 grid((vdim + GROUPS * CPT - 1) / (GROUPS * CPT), n_heads, n_seqs);
   const long blocks = (long)grid.x * grid.y * grid.z;
   constexpr bool three_fit = scan_smem<NPL>(PC, 3, CPT) <= 226 * 1024;      // a block's limit
   if constexpr (!three_fit)
-    return launch_scan<NPL, PC, VEC, 2, CPT>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
+    return launch_scan<NPL, PC, VEC, 2, CPT>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, token_decay, heads_per_qk, seq_row0,
                                              seq_slot, n_heads, dim, vdim, state, out);
   else if (blocks > fits(scan_smem<NPL>(PC, 3, CPT)) && blocks <= fits(scan_smem<NPL>(PC, 2, CPT)))
-    return launch_scan<NPL, PC, VEC, 2, CPT>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
+    return launch_scan<NPL, PC, VEC, 2, CPT>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, token_decay, heads_per_qk, seq_row0,
                                              seq_slot, n_heads, dim, vdim, state, out);
   else
-    return launch_scan<NPL, PC, VEC, 3, CPT>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
+    return launch_scan<NPL, PC, VEC, 3, CPT>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, token_decay, heads_per_qk, seq_row0,
                                              seq_slot, n_heads, dim, vdim, state, out);
 }
 
@@ -275,29 +287,31 @@ int g_force_cpt = 0;
 // B200, 2,048 tokens of one sequence, key size 128, 256 value channels a head: 8 heads (128 blocks
 // of two columns a thread) 238 us against 303 us with one column, 14 heads 324 against 506 us;
 // 6 heads of 64 x 64 (24 blocks) 173 against 156 us.
-template <int NPL, bool PC, bool VEC>
+template <int NPL, int PC, bool VEC>
 cudaError_t launch_scan_cols(int n_seqs, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off,
-                             int v_off, const float* decay, const float* head_decay, const int32_t* seq_row0,
+                             int v_off, const float* decay, const float* head_decay, const float* token_decay, int heads_per_qk, const int32_t* seq_row0,
                              const int32_t* seq_slot, int n_heads, int dim, int vdim, float* state, float* out) {
   const long blocks2 = (long)((vdim + 2 * GROUPS - 1) / (2 * GROUPS)) * n_heads * n_seqs;
   const bool two = g_force_cpt ? g_force_cpt == 2 : (NPL <= 8 && 2 * blocks2 >= sm_count());
   if (two)
     return launch_scan_staged<NPL, PC, VEC, (NPL <= 8 ? 2 : 1)>(n_seqs, stream, proj, ld, q_off, k_off, v_off, decay,
-                                                                 head_decay, seq_row0, seq_slot, n_heads, dim, vdim, state, out);
-  return launch_scan_staged<NPL, PC, VEC, 1>(n_seqs, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
+                                                                 head_decay, token_decay, heads_per_qk, seq_row0, seq_slot, n_heads, dim, vdim, state, out);
+  return launch_scan_staged<NPL, PC, VEC, 1>(n_seqs, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, token_decay, heads_per_qk, seq_row0,
                                              seq_slot, n_heads, dim, vdim, state, out);
 }
 
 }  // namespace
 
 extern "C" int sb_linrec_scan(const float* proj, int ld, int q_off, int k_off, int v_off, const float* decay,
-                              const float* head_decay, int n_seqs, const int32_t* seq_row0,
-                              const int32_t* seq_slot, int n_heads, int dim, int vdim, float* state,
-                              float* out, cudaStream_t stream) {
+                              const float* head_decay, const float* token_decay, int heads_per_qk, int n_seqs,
+                              const int32_t* seq_row0, const int32_t* seq_slot, int n_heads, int dim, int vdim,
+                              float* state, float* out, cudaStream_t stream) {
   if (n_seqs <= 0 || n_heads <= 0 || dim <= 0 || vdim <= 0 || !proj || !state || !out || !seq_row0 || !seq_slot)
     SB_FAIL(SB_ERR_ARG, "sb_linrec_scan: seqs=%d heads=%d dim=%d vdim=%d", n_seqs, n_heads, dim, vdim);
-  if ((decay == nullptr) == (head_decay == nullptr))
-    SB_FAIL(SB_ERR_ARG, "sb_linrec_scan: exactly one of the two kinds of decay is given");
+  if ((decay != nullptr) + (head_decay != nullptr) + (token_decay != nullptr) != 1)
+    SB_FAIL(SB_ERR_ARG, "sb_linrec_scan: exactly one of the three kinds of decay is given");
+  if (heads_per_qk <= 0 || n_heads % heads_per_qk)
+    SB_FAIL(SB_ERR_ARG, "sb_linrec_scan: %d heads do not share q and k in groups of %d", n_heads, heads_per_qk);
   if (dim > 32 * LANES) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_linrec_scan: key size %d is above %d", dim, 32 * LANES);
   if (n_heads > 65535 || n_seqs > 65535) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_linrec_scan: %d heads, %d sequences", n_heads, n_seqs);
   const int npl = (dim + LANES - 1) / LANES;
@@ -305,10 +319,11 @@ extern "C" int sb_linrec_scan(const float* proj, int ld, int q_off, int k_off, i
   const bool vec = dim % 4 == 0 && vdim % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && v_off % 4 == 0 &&
                    !((uintptr_t)proj & 15) && !((uintptr_t)decay & 15);
   cudaError_t e;
-#define SB_LINREC_ARGS n_seqs, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0, seq_slot, n_heads, dim, vdim, state, out
+#define SB_LINREC_ARGS n_seqs, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, token_decay, heads_per_qk, seq_row0, seq_slot, n_heads, dim, vdim, state, out
 #define SB_LINREC_LAUNCH(N)                                                                   \
-  e = decay ? (vec ? launch_scan_cols<N, true, true>(SB_LINREC_ARGS) : launch_scan_cols<N, true, false>(SB_LINREC_ARGS)) \
-            : (vec ? launch_scan_cols<N, false, true>(SB_LINREC_ARGS) : launch_scan_cols<N, false, false>(SB_LINREC_ARGS))
+  e = decay ? (vec ? launch_scan_cols<N, 1, true>(SB_LINREC_ARGS) : launch_scan_cols<N, 1, false>(SB_LINREC_ARGS)) \
+      : token_decay ? (vec ? launch_scan_cols<N, 2, true>(SB_LINREC_ARGS) : launch_scan_cols<N, 2, false>(SB_LINREC_ARGS)) \
+            : (vec ? launch_scan_cols<N, 0, true>(SB_LINREC_ARGS) : launch_scan_cols<N, 0, false>(SB_LINREC_ARGS))
   if (npl <= 1) SB_LINREC_LAUNCH(1);
   else if (npl <= 2) SB_LINREC_LAUNCH(2);
   else if (npl <= 4) SB_LINREC_LAUNCH(4);

@@ -314,7 +314,8 @@ __global__ void linrec_prep_kernel(float* proj, int ld, int q_off, int k_off, in
 // One warp per (row, head).
 template <typename TW, typename TO>
 __global__ void linrec_out_kernel(const float* o, const float* proj, int ld, int g_off, size_t n_items,
-                                  int n_heads, int vdim, const TW* __restrict__ norm_w, float eps, TO* out) {
+                                  int n_heads, int vdim, const TW* __restrict__ norm_w, int w_per_head,
+                                  int gate_sigmoid, float eps, TO* out) {
   sb_pdl_launch();
   sb_pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -329,8 +330,8 @@ __global__ void linrec_out_kernel(const float* o, const float* proj, int ld, int
   const float* g = proj + t * ld + g_off + (size_t)h * vdim;
   for (int j = lane; j < vdim; j += 32) {
     float v = src[j] * inv;
-    if (norm_w) v *= sb_to_f32<TW>(norm_w[j]);
-    out[item * vdim + j] = sb_from_f32<TO>(v * sb_silu(g[j]));
+    if (norm_w) v *= sb_to_f32<TW>(norm_w[(w_per_head ? (size_t)h * vdim : 0) + j]);
+    out[item * vdim + j] = sb_from_f32<TO>(gate_sigmoid ? v / (1.0f + expf(-g[j])) : v * sb_silu(g[j]));
   }
 }
 
@@ -456,8 +457,8 @@ extern "C" int sb_linrec_prep(float* proj, int n_rows, int ld, int q_off, int k_
 }
 
 extern "C" int sb_linrec_out(const float* o, const float* proj, int n_rows, int ld, int g_off, int n_heads,
-                             int vdim, const void* norm_w, int norm_w_dtype, float eps, void* out, int out_dtype,
-                             cudaStream_t stream) {
+                             int vdim, const void* norm_w, int norm_w_dtype, int w_per_head, int gate_sigmoid,
+                             float eps, void* out, int out_dtype, cudaStream_t stream) {
   if (n_rows <= 0 || n_heads <= 0 || vdim <= 0 || !o || !proj || !out)
     SB_FAIL(SB_ERR_ARG, "sb_linrec_out: rows=%d heads=%d vdim=%d", n_rows, n_heads, vdim);
   if (!sb_valid_dtype(out_dtype) || (norm_w && !sb_valid_dtype(norm_w_dtype)))
@@ -467,7 +468,7 @@ extern "C" int sb_linrec_out(const float* o, const float* proj, int n_rows, int 
   SB_DISPATCH_DTYPE(norm_w ? norm_w_dtype : SB_F32, TW, {
     SB_DISPATCH_DTYPE(out_dtype, TO, {
       sb_launch<SB_K_ELEMENTWISE>(linrec_out_kernel<TW, TO>, dim3(blocks), dim3(256), 0, stream, o, proj, ld, g_off,
-                                  items, n_heads, vdim, (const TW*)norm_w, eps, (TO*)out);
+                                  items, n_heads, vdim, (const TW*)norm_w, w_per_head, gate_sigmoid, eps, (TO*)out);
     });
   });
   SB_CHECK_LAUNCH("sb_linrec_out");

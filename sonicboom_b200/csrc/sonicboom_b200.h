@@ -246,18 +246,92 @@ int sb_linrec_prep(float* proj, int n_rows, int ld, int q_off, int k_off, int n_
                    const int32_t* row_pos, float* z, float inv_tau, const void* a2, const void* a2_bias,
                    int a2_dtype, int rank, int a1_off, sb_stream_t stream);
 /* S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head and sequence, token by token, from
- * and to state [slot, n_heads, vdim, dim] float32; a_t from decay [rows, n_heads * dim] or, one
- * value per head, from head_decay [n_heads] (exactly one of them).  out [rows, n_heads, vdim]. */
+ * and to state [slot, n_heads, vdim, dim] float32; a_t from decay [rows, n_heads * dim], or one
+ * fixed value per head from head_decay [n_heads], or one value per token and head from
+ * token_decay [rows, n_heads] (exactly one of the three).  heads_per_qk neighbouring heads read the
+ * same q and k (q and k then hold n_heads / heads_per_qk heads).  out [rows, n_heads, vdim]. */
 int sb_linrec_scan(const float* proj, int ld, int q_off, int k_off, int v_off, const float* decay,
-                   const float* head_decay, int n_seqs, const int32_t* seq_row0,
-                   const int32_t* seq_slot, int n_heads, int dim, int vdim, float* state,
-                   float* out, sb_stream_t stream);
+                   const float* head_decay, const float* token_decay, int heads_per_qk, int n_seqs,
+                   const int32_t* seq_row0, const int32_t* seq_slot, int n_heads, int dim, int vdim,
+                   float* state, float* out, sb_stream_t stream);
 void sb_linrec_force_columns(int cpt);   /* 1 or 2 columns per thread in sb_linrec_scan; 0: by the sizes */
-/* out [rows, n_heads * vdim] = o / sqrt(mean over vdim of o^2 + eps) * norm_w[vdim] (optional) *
- * silu(g), g at g_off of the projection row. */
+/* out [rows, n_heads * vdim] = o / sqrt(mean over vdim of o^2 + eps) * norm_w (optional: [vdim] for
+ * all heads, or [n_heads * vdim] with w_per_head) * gate(g), g at g_off of the projection row;
+ * the gate is silu, or the logistic function with gate_sigmoid. */
 int sb_linrec_out(const float* o, const float* proj, int n_rows, int ld, int g_off, int n_heads,
-                  int vdim, const void* norm_w, int norm_w_dtype, float eps, void* out, int out_dtype,
-                  sb_stream_t stream);
+                  int vdim, const void* norm_w, int norm_w_dtype, int w_per_head, int gate_sigmoid,
+                  float eps, void* out, int out_dtype, sb_stream_t stream);
+
+/* ---- rows that look at their neighbours in the sequence; the layer norm ----
+ * out[r] = table[tokens[r]] * scale + pair[i], i = (previous token * mul_prev + token * mul_cur) mod
+ * buckets, or i = buckets for a sequence's first token (pair has buckets + 1 rows).  The token before
+ * a step's first row comes from prev_token[slot]; sb_keep_last_token stores a step's last tokens there. */
+int sb_embed_pair(const int32_t* tokens, int n_rows, const int32_t* row_seq, const int32_t* row_pos,
+                  const int32_t* seq_row0, const int32_t* seq_slot, const int32_t* prev_token,
+                  const void* table, int table_dtype, int vocab, const void* pair, int buckets,
+                  int mul_prev, int mul_cur, int width, float scale, float* out, sb_stream_t stream);
+int sb_keep_last_token(const int32_t* tokens, const int32_t* seq_row0, const int32_t* seq_slot,
+                       int n_seqs, int32_t* prev_token, sb_stream_t stream);
+/* out[r] = (x - mean) / sqrt(var + eps) * weight over the row x[rows ? rows[r] : r] */
+int sb_layernorm(const float* x, const int32_t* rows, int n_rows, int width, const void* weight,
+                 int weight_dtype, float eps, void* out, int out_dtype, sb_stream_t stream);
+/* out[r, out_off + c] = act([x_t +] [bias +] sum_j w[c, j] x_(t - taps + 1 + j)) over the `channels`
+ * columns of x at x_off; taps before a step's first row of a sequence come from state [slot,
+ * taps - 1, channels] (float32), which then receives the step's last taps - 1 inputs; act 1: silu. */
+int sb_causal_conv(const float* x, int n_rows, int ld, int x_off, int channels, int taps, const void* w,
+                   const void* bias, int w_dtype, int act, int add_input, int n_seqs,
+                   const int32_t* row_seq, const int32_t* row_pos, const int32_t* seq_row0,
+                   const int32_t* seq_pos0, const int32_t* seq_slot, float* state, void* out,
+                   int out_dtype, int ld_out, int out_off, sb_stream_t stream);
+
+/* ---- the generalized delta rule ----
+ * aux [rows, 3, n_heads * dim] = decays exp(-decay_scale * sigmoid(w2 . tanh(proj[z_off : z_off + rank])
+ * + w0)) | sigmoid(proj[a_off ...] + a_bias) * u | u, u = k / sqrt(sum over the head of k^2 + key_eps). */
+int sb_delta_prep(const float* proj, int n_rows, int ld, int k_off, int a_off, int z_off, int n_heads,
+                  int dim, int rank, const void* w2, const void* w0, const void* a_bias, int w_dtype,
+                  float decay_scale, float key_eps, float* aux, sb_stream_t stream);
+/* S_t = diag(w) S_(t-1) - (a u)(u^T S_(t-1)) + k v^T, o_t = S_t^T r, from and to state [slot, n_heads,
+ * dim, dim] float32 (value channel by value channel); out [rows, n_heads, dim]. */
+int sb_delta_scan(const float* proj, int ld, int r_off, int k_off, int v_off, const float* aux, int n_seqs,
+                  const int32_t* seq_row0, const int32_t* seq_slot, int n_heads, int dim, float* state,
+                  float* out, sb_stream_t stream);
+
+/* ---- the state-space mixer's rows ----
+ * decay [rows, n_heads] = exp(-exp(a_log) dt), dt = softplus(proj[dt_off + h] + dt_bias); the row
+ * buffer's columns at xdt_off receive dt * (its columns at x_off). */
+int sb_ssd_prep(const float* proj, int n_rows, int ld_proj, int dt_off, float* xbc, int ld, int x_off,
+                int xdt_off, int n_heads, int vdim, const void* dt_bias, const void* a_log, int w_dtype,
+                float* decay, sb_stream_t stream);
+/* out [rows, n_heads * vdim] = rms over each of norm_groups equal parts of ((o + d_skip[h] x) silu(z)),
+ * times norm_w. */
+int sb_ssd_out(const float* o, const float* xbc, int n_rows, int ld, int x_off, const float* proj,
+               int ld_proj, int z_off, int n_heads, int vdim, int norm_groups, const void* d_skip,
+               const void* norm_w, int w_dtype, float eps, void* out, int out_dtype, sb_stream_t stream);
+
+/* ---- attention with logistic weights (see attn_sigmoid.cu) ---- */
+int sb_attention_sigmoid(const void* q, void* out, int act_dtype, int n_rows, const int32_t* row_seq,
+                         const int32_t* row_pos, const int32_t* page_off, const int32_t* page_ids,
+                         int page_size, const void* cache, int cache_dtype, int n_q_heads,
+                         int n_kv_heads, int hd, int window, int keep_first, float scale, float softcap,
+                         const float* head_bias, sb_stream_t stream);
+
+/* ---- mixture of experts (see moe.cu) ----
+ * ids, weights [rows, top]; order [pairs]; meta [1 + 3 * sb_moe_max_tiles]; w of sb_moe_up [experts, 2
+ * (gate, up), ff, width], of sb_moe_down [experts, width, ff]; act [pairs, ff] in the activation dtype
+ * (in grouped order); pair_out [pairs, width] float32 (in pair order). */
+int sb_moe_route(const float* logits, int n_rows, int n_experts, int top, int32_t* ids, float* weights,
+                 sb_stream_t stream);
+int sb_moe_max_tiles(int n_pairs, int n_experts);
+int sb_moe_group(const int32_t* ids, int n_pairs, int n_experts, int32_t* order, int32_t* meta,
+                 sb_stream_t stream);
+int sb_moe_up(const void* a, int a_dtype, const void* w, int w_dtype, const int32_t* order,
+              const int32_t* meta, int n_pairs, int n_experts, int top, int ff, int width, float limit,
+              float slope, void* act, sb_stream_t stream);
+int sb_moe_down(const void* act, int a_dtype, const void* w, int w_dtype, const int32_t* order,
+                const int32_t* meta, int n_pairs, int n_experts, int top, int width, int ff,
+                float* pair_out, sb_stream_t stream);
+int sb_moe_combine(float* x, const float* pair_out, const float* weights, int n_rows, int top, int width,
+                   sb_stream_t stream);
 
 int sb_sample_params_size(void);
 int sb_sample(float* logits, int n_rows, int vocab, const void* params, const int32_t* history,

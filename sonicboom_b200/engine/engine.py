@@ -19,7 +19,8 @@ class Engine:
         self.model = model
         self.use_decode_loop = True
         self.cache = Cache(model.kv_needs(), model.state_needs(), max_tokens,
-                           dtype=model.dtype, device=model.device, n_slots=n_slots)
+                           dtype=model.dtype, device=model.device, n_slots=n_slots,
+                           model_state=model.model_state_needs())
 
     def open(self) -> int:
         """A slot for a new sequence."""

@@ -35,14 +35,16 @@ class DecoderModel:
             if e.cache_from is not None:
                 mine = self.blocks[e.layer].kv_need()
                 theirs = self.blocks[spec.schedule[e.cache_from].layer].kv_need()
-                if mine != theirs:
+                # the mask may differ (the cache then keeps what the widest reader sees), the heads may not
+                if mine is None or theirs is None or \
+                        (mine.n_kv_heads, mine.head_dim) != (theirs.n_kv_heads, theirs.head_dim):
                     from ..config.specs import ConfigError
                     raise ConfigError(f"schedule[{i}] reads the cache of entry {e.cache_from}, "
                                       f"whose keys and values ({theirs}) are not what it needs ({mine})")
         # what joins the stream right before a schedule entry: {entry: StreamInjection}
         self.injections = {inj.before_entry: inj for inj in spec.injections}
         self.injection_vectors = {}
-        self.embedding = self.head = None
+        self.embedding = self.head = self.pair_table = None
 
     # ------------------------------------------------------------------ weights
     def tensor_requests(self) -> list[TensorRequest]:
@@ -53,6 +55,8 @@ class DecoderModel:
             if m is not None:
                 req += m.tensor_requests()
         req += self.final_norm.tensor_requests()
+        if s.pair_embedding is not None:
+            req.append(TensorRequest(s.pair_embedding.tensor, (s.pair_embedding.buckets + 1, s.width), "embedding"))
         req += [TensorRequest(inj.tensor, (inj.rows, s.width), "bias") for inj in s.injections if inj.tensor]
         req += [TensorRequest(name, tuple(shape), optional=True) for name, shape in s.unused_tensors]
         if s.head_tensor is not None:
@@ -64,6 +68,10 @@ class DecoderModel:
 
     def bind(self, get) -> None:
         self.embedding = get(self.spec.embedding_tensor)
+        if self.spec.pair_embedding is not None:
+            self.pair_table = get(self.spec.pair_embedding.tensor)
+            if self.pair_table.dtype != self.embedding.dtype:
+                self.pair_table, self.embedding = self.pair_table.float(), self.embedding.float()
         for b, m in zip(self.blocks, self.depth_mixes):
             b.bind(get)
             if m is not None:
@@ -79,12 +87,28 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ what the cache must hold
     def kv_needs(self) -> list:
-        """Per schedule entry: its KVNeed, or None when it reads another entry's cache."""
-        return [self.blocks[e.layer].kv_need() if e.cache_from is None else None
-                for e in self.spec.schedule]
+        """Per schedule entry: its KVNeed, or None when it reads another entry's cache.  An entry
+        whose cache others read keeps what the reader with the widest mask sees."""
+        from ..cache.kv import KVNeed
+        needs = [self.blocks[e.layer].kv_need() if e.cache_from is None else None
+                 for e in self.spec.schedule]
+        for e in self.spec.schedule:
+            if e.cache_from is None:
+                continue
+            mine, own = self.blocks[e.layer].kv_need(), needs[e.cache_from]
+            window = 0 if 0 in (mine.window, own.window) else max(mine.window, own.window)
+            needs[e.cache_from] = KVNeed(own.n_kv_heads, own.head_dim, window,
+                                         max(mine.keep_first, own.keep_first) if window else 0)
+        return needs
 
     def state_needs(self) -> list:
         return [self.blocks[e.layer].state_need() for e in self.spec.schedule]
+
+    def model_state_needs(self) -> dict:
+        """Named per-sequence state that belongs to no schedule entry: the last token a sequence was
+        fed, which a pair embedding hashes with the next one."""
+        from ..cache.kv import StateNeed
+        return {"prev_token": StateNeed((), torch.int32)} if self.spec.pair_embedding is not None else {}
 
     # ------------------------------------------------------------------ one step
     def forward(self, plan, cache) -> torch.Tensor:
@@ -99,8 +123,14 @@ class DecoderModel:
             if any(m is not None for m in mixes) else None
         x = streams[0] if streams is not None else \
             torch.empty((plan.n_rows, s.width), dtype=torch.float32, device=self.device)
-        ops.embed(plan.tokens, self.embedding, x, s.embedding_scale)
         ctx = StepContext(plan=plan, cache=cache)
+        if s.pair_embedding is None:
+            ops.embed(plan.tokens, self.embedding, x, s.embedding_scale)
+        else:
+            pe, prev = s.pair_embedding, ctx.model_state("prev_token")
+            ops.embed_pair(plan, prev, self.embedding, self.pair_table, pe.buckets, pe.mul_prev, pe.mul_cur, x,
+                           s.embedding_scale)
+            ops.keep_last_token(plan, prev)
         # an injection may add the embedding output again: it is then kept apart from the stream,
         # which blocks overwrite
         embedded = x if any(inj.embedding for inj in self.injections.values()) else None

@@ -843,15 +843,20 @@ def linrec_prep(proj: torch.Tensor, q_off: int, k_off: int, n_heads: int, dim: i
 
 def linrec_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, plan, n_heads: int, dim: int,
                 vdim: int, decay: torch.Tensor | None, head_decay: torch.Tensor | None,
-                state: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+                state: torch.Tensor, out: torch.Tensor, token_decay: torch.Tensor | None = None,
+                heads_per_qk: int = 1) -> torch.Tensor:
     """Walks every sequence's rows of the step through S = diag(a) S + k v^T, o = S^T q, from and
-    to the state rows of the sequences' slots (float32 [slots, heads, vdim, dim])."""
+    to the state rows of the sequences' slots (float32 [slots, heads, vdim, dim]).  The decay is
+    `decay` [rows, heads * dim], `head_decay` [heads] or `token_decay` [rows, heads]; `heads_per_qk`
+    neighbouring heads read the same q and k."""
     n, ld = proj.shape
     assert proj.dtype == torch.float32 and state.dtype == torch.float32 and out.dtype == torch.float32
     assert tuple(state.shape[1:]) == (n_heads, vdim, dim) and tuple(out.shape) == (n, n_heads, vdim)
     assert decay is None or (decay.dtype == torch.float32 and tuple(decay.shape) == (n, n_heads * dim))
     assert head_decay is None or (head_decay.dtype == torch.float32 and head_decay.numel() == n_heads)
-    _check(lib().sb_linrec_scan(_ptr(proj), ld, q_off, k_off, v_off, _ptr(decay), _ptr(head_decay), plan.n_seqs,
+    assert token_decay is None or (token_decay.dtype == torch.float32 and tuple(token_decay.shape) == (n, n_heads))
+    _check(lib().sb_linrec_scan(_ptr(proj), ld, q_off, k_off, v_off, _ptr(decay), _ptr(head_decay),
+                                _ptr(token_decay), heads_per_qk, plan.n_seqs,
                                 _i32(plan.seq_row0, "seq_row0"), _i32(plan.seq_slot, "seq_slot"), n_heads, dim,
                                 vdim, _ptr(state), _ptr(out), _stream()), "linrec_scan")
     return out
@@ -864,12 +869,190 @@ def force_linrec_columns(cpt: int) -> None:
 
 
 def linrec_out(o: torch.Tensor, proj: torch.Tensor, g_off: int, n_heads: int, vdim: int,
-               norm_w: torch.Tensor | None, eps: float, out: torch.Tensor) -> torch.Tensor:
-    """out [rows, heads * vdim] = rms(o) per head (optional weight [vdim]) * silu(g of the row)."""
+               norm_w: torch.Tensor | None, eps: float, out: torch.Tensor, gate: str = "silu") -> torch.Tensor:
+    """out [rows, heads * vdim] = rms(o) per head * weight (optional: [vdim] for all heads, or
+    [heads * vdim]) * gate(g of the row); the gate is "silu" or "sigmoid"."""
     n, ld = proj.shape
     assert tuple(o.shape) == (n, n_heads, vdim) and tuple(out.shape) == (n, n_heads * vdim)
-    assert g_off + n_heads * vdim <= ld and (norm_w is None or norm_w.numel() == vdim)
+    assert g_off + n_heads * vdim <= ld and (norm_w is None or norm_w.numel() in (vdim, n_heads * vdim))
+    assert gate in ("silu", "sigmoid")
+    per_head = norm_w is not None and n_heads > 1 and norm_w.numel() == n_heads * vdim
     _check(lib().sb_linrec_out(_ptr(o), _ptr(proj), n, ld, g_off, n_heads, vdim, _ptr(norm_w),
-                               _code(norm_w.dtype) if norm_w is not None else 0, ctypes.c_float(eps), _ptr(out),
+                               _code(norm_w.dtype) if norm_w is not None else 0, 1 if per_head else 0,
+                               1 if gate == "sigmoid" else 0, ctypes.c_float(eps), _ptr(out),
                                _code(out.dtype), _stream()), "linrec_out")
     return out
+
+
+# ---------------------------------------------------------------------- rows and their neighbours
+def embed_pair(plan, prev_token: torch.Tensor, table: torch.Tensor, pair: torch.Tensor, buckets: int,
+               mul_prev: int, mul_cur: int, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[r] = table[token] * scale + pair[(previous token * mul_prev + token * mul_cur) mod buckets],
+    row `buckets` of `pair` for a sequence's first token.  The token before a step's first row of a
+    sequence is `prev_token[slot]` (int32, one per slot); `keep_last_token` stores it."""
+    n, width = plan.n_rows, table.shape[1]
+    assert out.dtype == torch.float32 and tuple(out.shape) == (n, width) and table.dtype == pair.dtype
+    assert tuple(pair.shape) == (buckets + 1, width) and prev_token.dtype == torch.int32
+    _check(lib().sb_embed_pair(_i32(plan.tokens, "tokens"), n, _i32(plan.row_seq, "row_seq"),
+                               _i32(plan.row_pos, "row_pos"), _i32(plan.seq_row0, "seq_row0"),
+                               _i32(plan.seq_slot, "seq_slot"), _ptr(prev_token), _ptr(table), _code(table.dtype),
+                               table.shape[0], _ptr(pair), buckets, mul_prev, mul_cur, width,
+                               ctypes.c_float(scale), _ptr(out), _stream()), "embed_pair")
+    return out
+
+
+def keep_last_token(plan, prev_token: torch.Tensor) -> None:
+    """prev_token[slot] = the last token the step brings for the sequence in that slot."""
+    _check(lib().sb_keep_last_token(_i32(plan.tokens, "tokens"), _i32(plan.seq_row0, "seq_row0"),
+                                    _i32(plan.seq_slot, "seq_slot"), plan.n_seqs, _i32(prev_token, "prev_token"),
+                                    _stream()), "keep_last_token")
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+              rows: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r] = (x - mean) / sqrt(var + eps) * weight over the row x[rows[r]] or x[r] (no bias)."""
+    assert x.dtype == torch.float32 and x.dim() == 2
+    n, width = out.shape[0], x.shape[1]
+    assert out.shape[1] == width and weight.numel() == width and (rows is not None or x.shape[0] == n)
+    _check(lib().sb_layernorm(_ptr(x), _i32(rows, "rows") if rows is not None else _ptr(None), n, width,
+                              _ptr(weight), _code(weight.dtype), ctypes.c_float(eps), _ptr(out), _code(out.dtype),
+                              _stream()), "layernorm")
+    return out
+
+
+def causal_conv(x: torch.Tensor, x_off: int, channels: int, w: torch.Tensor, bias: torch.Tensor | None,
+                plan, state: torch.Tensor | None, out: torch.Tensor, out_off: int = 0, act: str = "none",
+                add_input: bool = False) -> torch.Tensor:
+    """out[r, out_off + c] = act([x +] [bias +] sum_j w[c, j] x_(t - taps + 1 + j)) on `channels`
+    columns of the float32 rows x from x_off; the taps before a step's first row of a sequence are
+    read from `state` [slot, taps - 1, channels] float32, which then takes the step's last inputs."""
+    n, ld = x.shape
+    taps = w.shape[1]
+    assert x.dtype == torch.float32 and tuple(w.shape) == (channels, taps) and out.shape[0] == n
+    assert bias is None or (bias.dtype == w.dtype and bias.numel() == channels)
+    assert act in ("none", "silu")
+    if taps > 1:
+        assert state.dtype == torch.float32 and tuple(state.shape[1:]) == (taps - 1, channels)
+    own = plan.n_rows == plan.n_seqs
+    _check(lib().sb_causal_conv(_ptr(x), n, ld, x_off, channels, taps, _ptr(w), _ptr(bias), _code(w.dtype),
+                                1 if act == "silu" else 0, 1 if add_input else 0, plan.n_seqs,
+                                _i32(plan.row_seq, "row_seq"), _i32(plan.row_pos, "row_pos"),
+                                _i32(plan.seq_row0, "seq_row0"), _i32(plan.seq_pos0, "seq_pos0"),
+                                _i32(plan.seq_slot, "seq_slot"), _ptr(state), _ptr(out), _code(out.dtype),
+                                out.shape[1], out_off, _stream()), "causal_conv",
+           launches=1 if own or taps == 1 else 2)
+    return out
+
+
+# ---------------------------------------------------------------------- the generalized delta rule
+def delta_prep(proj: torch.Tensor, k_off: int, a_off: int, z_off: int, n_heads: int, dim: int,
+               w2: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor, decay_scale: float, key_eps: float,
+               aux: torch.Tensor) -> torch.Tensor:
+    """aux [rows, 3, heads * dim] = decays exp(-decay_scale * sigmoid(w2 tanh(z1) + w0)) | removal
+    rates sigmoid(a + a_bias) times the unit key | the unit key k / sqrt(sum k^2 + key_eps)."""
+    n, ld = proj.shape
+    hk, rank = n_heads * dim, w2.shape[1]
+    assert proj.dtype == torch.float32 and aux.dtype == torch.float32 and tuple(aux.shape) == (n, 3, hk)
+    assert w2.shape[0] == hk and w0.numel() == hk and a_bias.numel() == hk and w2.dtype == w0.dtype == a_bias.dtype
+    _check(lib().sb_delta_prep(_ptr(proj), n, ld, k_off, a_off, z_off, n_heads, dim, rank, _ptr(w2), _ptr(w0),
+                               _ptr(a_bias), _code(w2.dtype), ctypes.c_float(decay_scale), ctypes.c_float(key_eps),
+                               _ptr(aux), _stream()), "delta_prep")
+    return aux
+
+
+def delta_scan(proj: torch.Tensor, r_off: int, k_off: int, v_off: int, aux: torch.Tensor, plan, n_heads: int,
+               dim: int, state: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """S = diag(w) S - (a u)(u^T S) + k v^T, o = S^T r per head, token by token, from and to the
+    state rows of the sequences' slots (float32 [slots, heads, dim, dim], value channel first)."""
+    n, ld = proj.shape
+    assert proj.dtype == torch.float32 and state.dtype == torch.float32 and out.dtype == torch.float32
+    assert tuple(state.shape[1:]) == (n_heads, dim, dim) and tuple(out.shape) == (n, n_heads, dim)
+    assert tuple(aux.shape) == (n, 3, n_heads * dim) and max(r_off, k_off, v_off) + n_heads * dim <= ld
+    _check(lib().sb_delta_scan(_ptr(proj), ld, r_off, k_off, v_off, _ptr(aux), plan.n_seqs,
+                               _i32(plan.seq_row0, "seq_row0"), _i32(plan.seq_slot, "seq_slot"), n_heads, dim,
+                               _ptr(state), _ptr(out), _stream()), "delta_scan")
+    return out
+
+
+# ---------------------------------------------------------------------- the state-space mixer's rows
+def ssd_prep(proj: torch.Tensor, dt_off: int, xbc: torch.Tensor, x_off: int, xdt_off: int, n_heads: int,
+             vdim: int, dt_bias: torch.Tensor, a_log: torch.Tensor, decay: torch.Tensor) -> torch.Tensor:
+    """decay [rows, heads] = exp(-exp(a_log) dt), dt = softplus(proj[dt_off + h] + dt_bias[h]); the
+    columns of `xbc` at xdt_off receive dt * (its columns at x_off)."""
+    n = proj.shape[0]
+    assert proj.dtype == xbc.dtype == decay.dtype == torch.float32 and tuple(decay.shape) == (n, n_heads)
+    assert dt_bias.dtype == a_log.dtype and dt_bias.numel() == a_log.numel() == n_heads and xbc.shape[0] == n
+    _check(lib().sb_ssd_prep(_ptr(proj), n, proj.shape[1], dt_off, _ptr(xbc), xbc.shape[1], x_off, xdt_off,
+                             n_heads, vdim, _ptr(dt_bias), _ptr(a_log), _code(a_log.dtype), _ptr(decay), _stream()),
+           "ssd_prep")
+    return decay
+
+
+def ssd_out(o: torch.Tensor, xbc: torch.Tensor, x_off: int, proj: torch.Tensor, z_off: int, n_heads: int,
+            vdim: int, norm_groups: int, d_skip: torch.Tensor, norm_w: torch.Tensor, eps: float,
+            out: torch.Tensor) -> torch.Tensor:
+    """out [rows, heads * vdim] = ((o + d_skip[h] x) silu(z)) / its root mean square over each of
+    `norm_groups` equal parts of the row, times norm_w."""
+    n, inner = o.shape[0], n_heads * vdim
+    assert o.dtype == xbc.dtype == proj.dtype == torch.float32 and o.numel() == n * inner
+    assert tuple(out.shape) == (n, inner) and d_skip.dtype == norm_w.dtype
+    assert d_skip.numel() == n_heads and norm_w.numel() == inner
+    _check(lib().sb_ssd_out(_ptr(o), _ptr(xbc), n, xbc.shape[1], x_off, _ptr(proj), proj.shape[1], z_off, n_heads,
+                            vdim, norm_groups, _ptr(d_skip), _ptr(norm_w), _code(norm_w.dtype), ctypes.c_float(eps),
+                            _ptr(out), _code(out.dtype), _stream()), "ssd_out")
+    return out
+
+
+# ---------------------------------------------------------------------- attention with logistic weights
+def attention_sigmoid(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache: torch.Tensor,
+                      n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, keep_first: int,
+                      scale: float, softcap: float, head_bias: torch.Tensor | None) -> torch.Tensor:
+    """Causal grouped-query attention whose weights are sigmoid(cap(q . k * scale) + head_bias[h]),
+    not normalised over the keys, over one cache entry's pages.  Key j is visible to the query at
+    position i when j <= i and (i - j < window or j < keep_first); window 0: every earlier key."""
+    n = q.shape[0]
+    g = plan.groups[group_index]
+    assert q.dtype == out.dtype and tuple(q.shape) == (n, n_q_heads, head_dim) and out.numel() == q.numel()
+    assert head_bias is None or (head_bias.dtype == torch.float32 and head_bias.numel() == n_q_heads)
+    _check(lib().sb_attention_sigmoid(
+        _ptr(q), _ptr(out), _code(q.dtype), n, _i32(plan.row_seq, "row_seq"), _i32(plan.row_pos, "row_pos"),
+        _i32(g.page_off, "page_off"), _i32(g.page_ids, "page_ids"), g.page_size, _ptr(cache), _code(cache.dtype),
+        n_q_heads, n_kv_heads, head_dim, window, keep_first, ctypes.c_float(scale), ctypes.c_float(softcap),
+        _ptr(head_bias), _stream()), "attention_sigmoid")
+    return out
+
+
+# ---------------------------------------------------------------------- mixture of experts
+def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """Per row of float32 logits [rows, experts]: the `top` largest (the lower index wins a tie) into
+    ids [rows, top] int32, and their softmax over the chosen ones into weights [rows, top]."""
+    n, e = logits.shape
+    assert logits.dtype == weights.dtype == torch.float32 and ids.dtype == torch.int32
+    assert tuple(ids.shape) == tuple(weights.shape) == (n, top)
+    _check(lib().sb_moe_route(_ptr(logits), n, e, top, _ptr(ids), _ptr(weights), _stream()), "moe_route")
+
+
+def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_up: torch.Tensor,
+                w_down: torch.Tensor, limit: float, slope: float, x: torch.Tensor) -> torch.Tensor:
+    """x[r] += sum over the row's choices k of weights[r, k] * expert ids[r, k] applied to h[r]; an
+    expert is down (g * sigmoid(slope g) * (u + 1)), g = min(gate h, limit), u = clamp(up h, +-limit).
+    w_up [experts, 2 (gate, up), ff, width], w_down [experts, width, ff], both in h's dtype."""
+    n, width = h.shape
+    top = ids.shape[1]
+    n_experts, _, ff, _ = w_up.shape
+    assert tuple(w_up.shape) == (n_experts, 2, ff, width) and tuple(w_down.shape) == (n_experts, width, ff)
+    assert h.dtype == w_up.dtype == w_down.dtype and x.dtype == torch.float32 and tuple(x.shape) == (n, width)
+    pairs = n * top
+    l = lib()
+    order = torch.empty(pairs, dtype=torch.int32, device=h.device)
+    meta = torch.empty(1 + 3 * int(l.sb_moe_max_tiles(pairs, n_experts)), dtype=torch.int32, device=h.device)
+    act = torch.empty((pairs, ff), dtype=h.dtype, device=h.device)
+    pair_out = torch.empty((pairs, width), dtype=torch.float32, device=h.device)
+    _check(l.sb_moe_group(_ptr(ids), pairs, n_experts, _ptr(order), _ptr(meta), _stream()), "moe_group")
+    _check(l.sb_moe_up(_ptr(h), _code(h.dtype), _ptr(w_up), _code(w_up.dtype), _ptr(order), _ptr(meta), pairs,
+                       n_experts, top, ff, width, ctypes.c_float(limit), ctypes.c_float(slope), _ptr(act),
+                       _stream()), "moe_up")
+    _check(l.sb_moe_down(_ptr(act), _code(act.dtype), _ptr(w_down), _code(w_down.dtype), _ptr(order), _ptr(meta),
+                         pairs, n_experts, top, width, ff, _ptr(pair_out), _stream()), "moe_down")
+    _check(l.sb_moe_combine(_ptr(x), _ptr(pair_out), _ptr(weights), n, top, width, _stream()), "moe_combine")
+    return x

@@ -86,9 +86,14 @@ class StepContext:
     def kv_group(self) -> int:
         return self.cache.group_of_entry[self.kv_entry]
 
-    def state(self) -> torch.Tensor:
-        """[slot, ...] state tensor of the running entry; rows are `plan.seq_slot`."""
-        return self.cache.state[self.entry]
+    def state(self, name: Optional[str] = None) -> torch.Tensor:
+        """[slot, ...] state tensor of the running entry (the one called `name`, when the entry
+        asked for several by name); rows are `plan.seq_slot`."""
+        return self.cache.state[self.entry if name is None else (self.entry, name)]
+
+    def model_state(self, name: str) -> torch.Tensor:
+        """[slot, ...] state tensor that the model as a whole asked for under `name`."""
+        return self.cache.state[("model", name)]
 
 
 class Part:

@@ -3,18 +3,60 @@ x2 = ffn(f) + x1 (core/src/model/emit.cpp:436-459 with no post norms, gate or ou
 as the reference's traits set for this architecture: core/src/model/recipe.cpp:65-70)."""
 from __future__ import annotations
 
-from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, make, register_block)
+import torch
+
+from .. import ops
+from ..cache.kv import StateNeed
+from ..weights.loader import TensorRequest
+from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Part, make, register_block)
+
+
+class InputConv(Part):
+    """h <- h + conv(h): a short causal convolution over time on every channel of what a sublayer
+    reads, added to it.  The last taps - 1 inputs of every sequence are state of the cache, under
+    `state_name` of the running entry."""
+
+    def __init__(self, spec, state_name, dtype):
+        self.spec, self.state_name, self.dtype = spec, state_name, dtype
+        self.weight = None
+
+    def tensor_requests(self):
+        return [TensorRequest(self.spec.tensor, (self.spec.width, self.spec.taps), "bias")]
+
+    def bind(self, get):
+        self.weight = get(self.spec.tensor)
+
+    def state_need(self):
+        return StateNeed((self.spec.taps - 1, self.spec.width), torch.float32) if self.spec.taps > 1 else None
+
+    def forward(self, h, ctx):
+        """h: float32 normed rows; returns h + conv(h) in the activation dtype."""
+        out = torch.empty(h.shape, dtype=self.dtype, device=h.device)
+        state = ctx.state(self.state_name) if self.spec.taps > 1 else None
+        return ops.causal_conv(h, 0, self.spec.width, self.weight, None, ctx.plan, state, out, add_input=True)
 
 
 @register_block("pre_norm")
 class PreNormBlock(Block):
+    """h = norm(x); x1 = mix(h) + x; f = norm(x1); x2 = ffn(f) + x1 (without a feed-forward the
+    result is x1).  With `mixer_conv` / `feed_forward_conv` in the spec, what a sublayer reads
+    passes a short causal convolution first: the norm then writes float32 rows and the
+    convolution's kernel hands the sublayer its rows in the activation dtype."""
+
     def __init__(self, spec, dtype, device):
         self.dtype = dtype
         self.mixer_norm = make(NORMS, "norm", spec.mixer_norm, dtype, device)
         self.mixer = make(MIXERS, "mixer", spec.mixer, dtype, device)
-        self.feed_forward_norm = make(NORMS, "norm", spec.feed_forward_norm, dtype, device)
-        self.feed_forward = make(FEED_FORWARDS, "feed-forward", spec.feed_forward, dtype, device)
-        self.parts = [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        self.parts = [self.mixer_norm, self.mixer]
+        self.feed_forward = self.feed_forward_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward_norm = make(NORMS, "norm", spec.feed_forward_norm, dtype, device)
+            self.feed_forward = make(FEED_FORWARDS, "feed-forward", spec.feed_forward, dtype, device)
+            self.parts += [self.feed_forward_norm, self.feed_forward]
+        self.mixer_conv = InputConv(spec.mixer_conv, "conv1", dtype) if spec.mixer_conv is not None else None
+        self.feed_forward_conv = InputConv(spec.feed_forward_conv, "conv2", dtype) \
+            if spec.feed_forward_conv is not None and self.feed_forward is not None else None
+        self.parts += [c for c in (self.mixer_conv, self.feed_forward_conv) if c is not None]
 
     def tensor_requests(self):
         return [r for p in self.parts for r in p.tensor_requests()]
@@ -27,25 +69,41 @@ class PreNormBlock(Block):
         return self.mixer.kv_need()
 
     def state_need(self):
-        return self.mixer.state_need()
+        """The mixer's state; with input convolutions, a dict that also names theirs."""
+        need = self.mixer.state_need()
+        convs = {c.state_name: c.state_need() for c in (self.mixer_conv, self.feed_forward_conv)
+                 if c is not None and c.state_need() is not None}
+        if not convs:
+            return need
+        if need is not None:
+            convs.update(need if isinstance(need, dict) else {None: need})
+        return convs
 
     def input_norm(self):
-        return self.mixer_norm
+        return self.mixer_norm if self.mixer_conv is None else None     # a convolution wants float32 rows
 
     def first_weights(self, rows):
         return self.mixer.first_weights(rows)
 
+    def _read(self, norm, conv, x, ctx):
+        """What a sublayer reads of the stream x."""
+        if conv is not None:
+            ctx.take_normed(norm, x)
+            return conv.forward(norm.forward(x, torch.float32), ctx)
+        h = ctx.take_normed(norm, x)
+        return h if h is not None else norm.forward(x, self.dtype)
+
     def forward(self, x, ctx):
-        h = ctx.take_normed(self.mixer_norm, x)
-        if h is None:
-            h = self.mixer_norm.forward(x, self.dtype)
-        ctx.next_norm = self.feed_forward_norm
+        after, after_weights = ctx.after_block_norm, ctx.after_block_weights
+        h = self._read(self.mixer_norm, self.mixer_conv, x, ctx)
+        if self.feed_forward is None:
+            ctx.next_norm, ctx.next_weights = after, after_weights
+            return self.mixer.forward(h, ctx, residual=x)
+        ctx.next_norm = self.feed_forward_norm if self.feed_forward_conv is None else None
         x = self.mixer.forward(h, ctx, residual=x)
-        f = ctx.take_normed(self.feed_forward_norm, x)
-        if f is None:
-            f = self.feed_forward_norm.forward(x, self.dtype)
+        f = self._read(self.feed_forward_norm, self.feed_forward_conv, x, ctx)
         # the block's result is the feed-forward's, so what follows the block follows its product
-        ctx.next_norm, ctx.next_weights = ctx.after_block_norm, ctx.after_block_weights
+        ctx.next_norm, ctx.next_weights = after, after_weights
         return self.feed_forward.forward(f, ctx, residual=x)
 
 

@@ -12,7 +12,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorRequest
-from .base import FeedForward, register_feed_forward
+from .base import FEED_FORWARDS, FeedForward, make, register_feed_forward
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -148,3 +148,71 @@ class PolyNormFF(FeedForward):
         return ctx.linear(t, self.w_down, out,
                           ops.EPI_RESIDUAL if residual is not None else ops.EPI_NONE,
                           residual=residual, act_dtype=self.dtype)
+
+
+@register_feed_forward("experts_glu_clamped")
+class ExpertsClampedGLU(FeedForward):
+    """Mixture of experts over clamped gated feed-forwards (the form of `glu_clamped`): router logits
+    z = R h + b in float32; each token goes through the `top` experts with the largest logits (the
+    lower index wins a tie), weighted by the softmax over the chosen logits only; a shared expert
+    (`shared`, a feed-forward spec of its own, or None) runs for every token and is added.
+    `params`: `experts`, `top`, `limit`, `slope`, `shared`.  Tensors after the prefix: router
+    [experts, width], router.b [experts], e<j>.gate, e<j>.up [intermediate, width], e<j>.down [width,
+    intermediate]; the shared expert's under its own prefix.
+
+    The experts' matrices are stacked when bound, [experts, gate | up, intermediate, width] and
+    [experts, width, intermediate]; a step groups its (token, choice) pairs by expert on the device
+    and walks them in tiles of one expert, so no expert's matrix is read for tokens that did not
+    choose it and nothing comes back to the host."""
+
+    def __init__(self, spec, dtype, device):
+        from ..config.specs import ConfigError
+        self.spec, self.dtype = spec, dtype
+        p = dict(spec.params)
+        self.n_experts, self.top = int(p.get("experts", 0)), int(p.get("top", 0))
+        self.limit, self.slope = float(p.get("limit", 0.0)), float(p.get("slope", 1.0))
+        if not 0 < self.top <= self.n_experts:
+            raise ConfigError(f"a mixture of {self.n_experts} experts cannot choose {self.top}")
+        if not self.limit > 0.0:
+            raise ConfigError(f"feed-forward limit {self.limit} must be positive")
+        shared = p.get("shared")
+        self.shared = make(FEED_FORWARDS, "feed-forward", shared, dtype, device) if shared is not None else None
+        self.w_router = self.b_router = self.w_up = self.w_down = None
+
+    def tensor_requests(self):
+        p, d, ff = self.spec.prefix, self.spec.width, self.spec.intermediate
+        req = [TensorRequest(p + "router", (self.n_experts, d)), TensorRequest(p + "router.b", (self.n_experts,), "bias")]
+        for j in range(self.n_experts):
+            req += [TensorRequest(f"{p}e{j}.gate", (ff, d)), TensorRequest(f"{p}e{j}.up", (ff, d)),
+                    TensorRequest(f"{p}e{j}.down", (d, ff))]
+        return req + (self.shared.tensor_requests() if self.shared is not None else [])
+
+    def bind(self, get):
+        p = self.spec.prefix
+        self.w_router, self.b_router = get(p + "router"), get(p + "router.b")
+        ups = [torch.stack([get(f"{p}e{j}.gate"), get(f"{p}e{j}.up")]) for j in range(self.n_experts)]
+        downs = [get(f"{p}e{j}.down") for j in range(self.n_experts)]
+        kept = {t.dtype for t in ups + downs}
+        if len(kept) > 1:
+            ups, downs = [t.float() for t in ups], [t.float() for t in downs]
+        self.w_up, self.w_down = torch.stack(ups).contiguous(), torch.stack(downs).contiguous()
+        if self.shared is not None:
+            self.shared.bind(get)
+
+    def forward(self, h, ctx, residual=None):
+        rows = h.shape[0]
+        # what follows this part follows its last kernel, which is not a product: nothing rides on one
+        ctx.next_norm = ctx.next_weights = None
+        logits = torch.empty((rows, self.n_experts), dtype=torch.float32, device=h.device)
+        ops.linear(h, self.w_router, logits, ops.EPI_BIAS, bias=self.b_router)
+        ids = torch.empty((rows, self.top), dtype=torch.int32, device=h.device)
+        weights = torch.empty((rows, self.top), dtype=torch.float32, device=h.device)
+        ops.moe_route(logits, self.top, ids, weights)
+        if self.shared is not None:
+            out = self.shared.forward(h, ctx, residual=residual)
+        elif residual is not None:
+            out = residual
+        else:
+            out = torch.zeros((rows, self.spec.width), dtype=torch.float32, device=h.device)
+        a = h if h.dtype == self.w_up.dtype else ops.cast(h, self.w_up.dtype)
+        return ops.moe_experts(a, ids, weights, self.w_up, self.w_down, self.limit, self.slope, out)

@@ -55,3 +55,25 @@ class OnePlusRMSNorm(RMSNorm):
 
     def bind(self, get):
         self.weight = (get(self.tensor).float() + 1.0).contiguous()
+
+
+@register_norm("layernorm")
+class LayerNorm(Norm):
+    """Layer norm with a weight and no bias: y = (x - mean) / sqrt(var + eps) * w, the variance
+    being the mean of the squared deviations.  It is not an RMS norm, so no product kernel
+    applies it to its own result (`as_rms` is None) and it runs as a kernel of its own."""
+
+    def __init__(self, spec, dtype, device):
+        self.width, self.eps, self.tensor = spec.width, float(spec.eps), spec.tensor
+        self.weight = None
+
+    def tensor_requests(self):
+        return [TensorRequest(self.tensor, (self.width,), "norm")]
+
+    def bind(self, get):
+        self.weight = get(self.tensor)
+
+    def forward(self, x, out_dtype, rows=None):
+        n = x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.width), dtype=out_dtype, device=x.device)
+        return ops.layernorm(x, self.weight, self.eps, out, rows)

@@ -5,6 +5,7 @@ sizes of Qwen2.5-7B with random weights on one B200.
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --arch zolulix [--sizes w2048,w3584] [--prompt 2048] [--batch 8] [--steps K]
     python bench.py --arch mefupel [--sizes w2048,w3584] [--prompt 2048] [--batch 8] [--steps K]
+    python bench.py --arch leguvik [--sizes w2048,w3584] [--prompt 2048] [--batch 8] [--steps K]
 
 Prints ONE JSON line.  (`--arch zolulix` is a measurement of its own: the Zolulix design beside the
 Qwen2.5 decoder of equal sizes and its kernels alone; without it the workload below runs.)  A "step" is one decode step of the whole batch.  The default run is a
@@ -760,6 +761,224 @@ def run_mefupel(args) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------- --arch leguvik
+def leguvik_config(width, n_layers, vocab, heads, kv_heads, dim, window, keep_first, s_heads, s_vdim, s_state,
+                   d_heads, d_dim, experts, top, expert_ff, shared_ff, rank=32, taps=4):
+    """A Leguvik model of the given layer sizes: delta rule, attention, state space, state space,
+    delta rule, attention over the first attention layer's keys, state space, and so on in turn,
+    every layer with a mixture of experts and a shared expert, input convolutions and the pair
+    embedding."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+           "mask": {"size": window, "keep_first": keep_first}}
+    kinds = [("general_delta", {"heads": d_heads, "dim": d_dim, "decay_rank": rank}), ("attention", att),
+             ("mamba2", {"heads": s_heads, "vdim": s_vdim, "state": s_state, "groups": 1, "norm_groups": 1, "conv": 4}),
+             ("mamba2", {"heads": s_heads, "vdim": s_vdim, "state": s_state, "groups": 1, "norm_groups": 1, "conv": 4}),
+             ("general_delta", {"heads": d_heads, "dim": d_dim, "decay_rank": rank}),
+             ("attention", dict(att, kv_from=1)),
+             ("mamba2", {"heads": s_heads, "vdim": s_vdim, "state": s_state, "groups": 1, "norm_groups": 1, "conv": 4})]
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff, "limit": 7.0},
+           "shared": {"ff": shared_ff, "limit": 7.0}}
+    layers = []
+    for i in range(n_layers):
+        kind, mixer = kinds[i % 7]
+        mixer = dict(mixer)
+        if "kv_from" in mixer:
+            mixer["kv_from"] = i - 4
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Leguvik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "canon": {"taps": taps},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 36313, "mul_cur": 27191}},
+            "logit_softcap": 30.0, "layers": layers}
+
+
+LEGUVIK_SIZES = {
+    # name: Leguvik sizes; the Mefupel model beside it has the same width, depth and vocabulary, its
+    # feed-forward as wide as what a Leguvik token uses (top * expert_ff + shared_ff), the same
+    # attention heads and window, and recurrent heads of the delta rule's count and size
+    "w2048": dict(width=2048, n_layers=7, vocab=32768, heads=16, kv_heads=4, dim=128, window=1024, keep_first=64,
+                  s_heads=64, s_vdim=64, s_state=128, d_heads=32, d_dim=64, experts=32, top=4, expert_ff=1024,
+                  shared_ff=2048),
+    "w3584": dict(width=3584, n_layers=7, vocab=32768, heads=28, kv_heads=4, dim=128, window=4096, keep_first=128,
+                  s_heads=112, s_vdim=64, s_state=128, d_heads=56, d_dim=64, experts=64, top=6, expert_ff=1536,
+                  shared_ff=3072),
+}
+
+
+def leguvik_kernels(bench, z, rows, context):
+    """Each kernel that came with Leguvik alone at `rows` rows (one sequence of `rows` tokens when
+    rows > 64, else `rows` sequences that hold `context` tokens each and go on by one), with the
+    bytes it must read and write once, and beside each the like kernel of the framework's other
+    models at the same sizes."""
+    import torch
+    from sonicboom_b200 import ops
+    from sonicboom_b200.cache.kv import Cache, KVNeed, StateNeed
+    from sonicboom_b200.engine.step import StepEntry, StepPlan
+    dev, pk, timed = bench.dev, bench.pk, bench.timed
+    W = z["width"]
+    f32, bf = torch.float32, torch.bfloat16
+    out = {}
+
+    def rec(name, ms, nbytes, flops=0):
+        out[name] = {"us": round(ms * 1e3, 2), "bytes": int(nbytes),
+                     "hbm_frac": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 3)}
+        if flops:
+            out[name]["tflops"] = round(flops / (ms / 1e3) / 1e12, 2)
+    prompt = rows > 64
+    n_seqs, new = (1, rows) if prompt else (rows, 1)
+    past = 0 if prompt else context
+    H, G, d, win, keep = z["heads"], z["kv_heads"], z["dim"], z["window"], z["keep_first"]
+    sh, sv, sn = z["s_heads"], z["s_vdim"], z["s_state"]
+    dh, dd = z["d_heads"], z["d_dim"]
+    inner, hk = sh * sv, dh * dd
+    channels = inner + 2 * sn
+    needs = {None: StateNeed((sh, sv, sn)), "conv": StateNeed((3, channels)), "canon": StateNeed((3, W)),
+             "delta": StateNeed((dh, dd, dd)), "gla": StateNeed((dh, dd, dd))}
+    cache = Cache([KVNeed(G, d, win, keep), KVNeed(G, d, win, 0)], [needs, None], n_seqs * (past + new + 64), bf, dev,
+                  n_slots=n_seqs, model_state={"prev_token": StateNeed((), torch.int32)})
+    slots = [cache.open() for _ in range(n_seqs)]
+    for s in slots:
+        if past:
+            cache.reserve(s, past)
+            cache.advance(s, past)
+        cache.reserve(s, past + new)
+    toks = torch.randint(0, z["vocab"], (new,), generator=bench.gen).tolist()
+    plan = StepPlan(cache, [StepEntry(s, toks, []) for s in slots], dev)
+    kind = f"{n_seqs} sequence(s) of {new}" + (f" after {past}" if past else "")
+    # rows of the stream
+    x = torch.randn(rows, W, device=dev)
+    wn = torch.ones(W, device=dev, dtype=bf)
+    nf, nb = torch.empty(rows, W, device=dev), torch.empty(rows, W, device=dev, dtype=bf)
+    rec("layernorm (float32 rows out)", timed(lambda: ops.layernorm(x, wn, 1e-5, nf)), rows * W * 8)
+    rec("like: rmsnorm (bfloat16 rows out)", timed(lambda: ops.rmsnorm(x, wn, 1e-5, nb)), rows * W * 6)
+    cw = torch.randn(W, 4, device=dev).to(bf)
+    rec("causal_conv, added to its input (4 taps)",
+        timed(lambda: ops.causal_conv(nf, 0, W, cw, None, plan, cache.state[(0, "canon")], nb, add_input=True)),
+        rows * W * 6)
+    table = torch.randn(z["vocab"], W, device=dev).to(bf)
+    pair = torch.randn(65522, W, device=dev).to(bf)
+    rec("embed_pair", timed(lambda: ops.embed_pair(plan, cache.state[("model", "prev_token")], table, pair, 65521,
+                                                   36313, 27191, nf)), rows * W * 8)
+    # attention
+    g0, store0 = plan.groups[cache.group_of_entry[0]], cache.groups[cache.group_of_entry[0]].entry_storage(0)
+    g1, store1 = plan.groups[cache.group_of_entry[1]], cache.groups[cache.group_of_entry[1]].entry_storage(1)
+    store0.normal_()
+    store1.normal_()
+    q = torch.randn(rows, H, d, device=dev).to(bf)
+    o = torch.empty(rows, H * d, device=dev, dtype=bf)
+    pb = torch.zeros(H, device=dev)
+    if prompt:
+        keys = sum(min(i + 1, win) + min(keep, max(0, i + 1 - win)) for i in range(rows))
+        kv_bytes = rows * G * d * 4
+    else:
+        keys = rows * (min(past + 1, win) + min(keep, max(0, past + 1 - win)))
+        kv_bytes = keys * G * d * 4
+    att_bytes, att_flops = kv_bytes + rows * H * d * 4, 4 * keys * H * d
+    rec(f"attention_sigmoid ({kind}; window {win}, {keep} first keys kept)",
+        timed(lambda: ops.attention_sigmoid(q, o, plan, cache.group_of_entry[0], store0, H, G, d, win, keep,
+                                            d ** -0.5, 30.0, pb)), att_bytes, att_flops)
+    rec(f"like: attention, softmax ({kind}; window {win})",
+        timed(lambda: ops.attention(q, o, plan, cache.group_of_entry[1], store1, H, G, d, win, d ** -0.5)),
+        att_bytes, att_flops)
+    # delta rule
+    rank = 32
+    dproj = torch.randn(rows, 5 * hk + rank, device=dev) * 0.1
+    w2, w0, ab = (torch.randn(hk, rank, device=dev).to(bf), torch.zeros(hk, device=dev, dtype=bf),
+                  torch.zeros(hk, device=dev, dtype=bf))
+    aux = torch.empty(rows, 3, hk, device=dev)
+    rec("delta_prep", timed(lambda: ops.delta_prep(dproj, hk, 4 * hk, 5 * hk, dh, dd, w2, w0, ab, 0.6065, 1e-6, aux)),
+        rows * hk * 20)
+    do = torch.empty(rows, dh, dd, device=dev)
+    dstate = cache.state[(0, "delta")]
+    scan_bytes = rows * hk * 4 * 7 + 8 * n_seqs * dh * dd * dd
+    rec(f"delta_scan ({kind}; {dh} heads of {dd} x {dd})",
+        timed(lambda: ops.delta_scan(dproj, 0, hk, 2 * hk, aux, plan, dh, dd, dstate, do)), scan_bytes,
+        10 * rows * dh * dd * dd)
+    decay = torch.rand(rows, hk, device=dev) * 0.1 + 0.9
+    rec(f"like: linrec_scan, a decay per channel ({kind}; {dh} heads of {dd} x {dd})",
+        timed(lambda: ops.linrec_scan(dproj, 0, hk, 2 * hk, plan, dh, dd, dd, decay, None, cache.state[(0, "gla")], do)),
+        rows * hk * 4 * 5 + 8 * n_seqs * dh * dd * dd, 6 * rows * dh * dd * dd)
+    # state space
+    sproj = torch.randn(rows, 2 * inner + 2 * sn + sh, device=dev) * 0.1
+    xbc = torch.empty(rows, channels + inner, device=dev)
+    scw, scb = torch.randn(channels, 4, device=dev).to(bf), torch.zeros(channels, device=dev, dtype=bf)
+    rec("causal_conv with silu (x | B | C, 4 taps)",
+        timed(lambda: ops.causal_conv(sproj, inner, channels, scw, scb, plan, cache.state[(0, "conv")], xbc, act="silu")),
+        rows * channels * 8)
+    dtb, alog, dsk = (torch.zeros(sh, device=dev, dtype=bf), torch.zeros(sh, device=dev, dtype=bf),
+                      torch.ones(sh, device=dev, dtype=bf))
+    tdec = torch.empty(rows, sh, device=dev)
+    rec("ssd_prep", timed(lambda: ops.ssd_prep(sproj, inner + channels, xbc, 0, channels, sh, sv, dtb, alog, tdec)),
+        rows * inner * 8)
+    so = torch.empty(rows, sh, sv, device=dev)
+    rec(f"linrec_scan, a decay per token and head ({kind}; {sh} heads of {sn} x {sv}, keys and queries shared)",
+        timed(lambda: ops.linrec_scan(xbc, inner + sn, inner, channels, plan, sh, sn, sv, None, None, cache.state[0], so,
+                                      token_decay=tdec, heads_per_qk=sh)),
+        rows * 4 * (2 * sn + 2 * inner + sh) + 8 * n_seqs * sh * sv * sn, 6 * rows * sh * sv * sn)
+    mixed = torch.empty(rows, inner, device=dev, dtype=bf)
+    snw = torch.ones(inner, device=dev, dtype=bf)
+    rec("ssd_out", timed(lambda: ops.ssd_out(so, xbc, 0, sproj, 0, sh, sv, 1, dsk, snw, 1e-5, mixed)), rows * inner * 14)
+    # experts
+    E, top, eff = z["experts"], z["top"], z["expert_ff"]
+    h = torch.randn(rows, W, device=dev).to(bf)
+    logits = torch.randn(rows, E, device=dev)
+    ids, wts = torch.empty(rows, top, dtype=torch.int32, device=dev), torch.empty(rows, top, device=dev)
+    rec("moe_route", timed(lambda: ops.moe_route(logits, top, ids, wts)), rows * (E * 4 + top * 8))
+    w_up = torch.randn(E, 2, eff, W, device=dev).to(bf) * 0.02
+    w_down = torch.randn(E, W, eff, device=dev).to(bf) * 0.02
+    used = min(E, rows * top)
+    moe_bytes = used * 3 * eff * W * 2 + rows * W * 10 + rows * top * (eff * 4 + W * 8)
+    moe_flops = 6 * rows * top * eff * W
+    rec(f"moe_experts: group, up, down, combine ({E} experts of {eff}, {top} a row)",
+        timed(lambda: ops.moe_experts(h, ids, wts, w_up, w_down, 7.0, 1.702, x)), moe_bytes, moe_flops)
+    ff = top * eff
+    wgu = torch.randn(2 * ff, W, device=dev).to(bf) * 0.02
+    wd = torch.randn(W, ff, device=dev).to(bf) * 0.02
+    act = torch.empty(rows, ff, device=dev, dtype=bf)
+
+    def dense():
+        ops.linear(h, wgu, act, ops.EPI_SWIGLU, gate=(7.0, 1.702))
+        ops.linear(act, wd, x, ops.EPI_RESIDUAL, residual=x)
+    rec(f"like: dense gated feed-forward of the same {ff} values a row (two products)", timed(dense),
+        3 * ff * W * 2 + rows * W * 10 + rows * ff * 4, moe_flops)
+    return out
+
+
+def run_leguvik(args) -> int:
+    """Prefill and decode throughput of Leguvik models at layer sizes of real models (random
+    weights) beside the Mefupel models of equal width, depth, vocabulary and feed-forward values a
+    token; and each of its kernels alone beside the like kernels of the other models."""
+    import torch
+    import sonicboom_b200 as sb
+    from sonicboom_b200 import ops
+
+    bench = ArchBench()
+    dev = bench.dev
+    result = {"arch": "leguvik", "impl": "ours", "dtype": "bf16", "peaks": bench.pk, "sizes": {},
+              "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
+              "timing": "CUDA events; kernels alone: median of 5 after 3 warm-up calls, L2 flushed "
+                        "(256 MB written) before each; models: prefill median of 3, decode one region of K steps"}
+    with ClockSampler() as clocks:
+        for name, z in LEGUVIK_SIZES.items():
+            if args.sizes and name not in args.sizes.split(","):
+                continue
+            mz = dict(width=z["width"], n_layers=z["n_layers"], ff=z["top"] * z["expert_ff"] + z["shared_ff"],
+                      vocab=z["vocab"], heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], window=z["window"],
+                      r_heads=z["d_heads"], r_dim=z["d_dim"], r_vdim=z["d_dim"])
+            rec = {"leguvik_config": dict(z)}
+            for label, cfg in (("leguvik", leguvik_config(**z)),
+                               ("mefupel (equal width, layers, vocab, feed-forward values a token)", mefupel_config(**mz))):
+                m = sb.random_model(cfg, seed=0, dtype="bfloat16", device=dev, std=0.02)
+                rec[label] = bench.model_points(m, args.prompt, args.batch, args.steps, args.warmup)
+                del m
+                torch.cuda.empty_cache()
+            for rows in (args.prompt, args.batch):
+                rec["kernels_rows_%d" % rows] = leguvik_kernels(bench, z, rows, args.prompt)
+            result["sizes"][name] = rec
+    ops.check_status()
+    result["clocks"] = clocks.summary()
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -779,13 +998,14 @@ def main() -> int:
                     help="run one phase only and print a short line (small cases for profilers)")
     ap.add_argument("--eager", action="store_true",
                     help="with --only decode: launch the step kernel by kernel, not as a graph")
-    ap.add_argument("--arch", choices=["qwen2", "zolulix", "mefupel"], default="qwen2",
+    ap.add_argument("--arch", choices=["qwen2", "zolulix", "mefupel", "leguvik"], default="qwen2",
                     help="zolulix: that design's prefill and decode throughput and its kernels alone, "
                          "beside the Qwen2.5 decoder of equal sizes (its own JSON line; the default "
                          "workload is unchanged); mefupel: the same for that design, beside Zolulix and "
-                         "Qwen2.5 models of equal sizes")
-    ap.add_argument("--sizes", default="", help="with --arch zolulix / mefupel: which of its sizes to run (comma separated)")
-    ap.add_argument("--prompt", type=int, default=2048, help="with --arch zolulix / mefupel: prompt length")
+                         "Qwen2.5 models of equal sizes; leguvik: the same for that design, beside Mefupel "
+                         "models of equal sizes")
+    ap.add_argument("--sizes", default="", help="with --arch zolulix / mefupel / leguvik: which of its sizes to run (comma separated)")
+    ap.add_argument("--prompt", type=int, default=2048, help="with --arch zolulix / mefupel / leguvik: prompt length")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -798,6 +1018,8 @@ def main() -> int:
         return run_zolulix(args)
     if args.arch == "mefupel":
         return run_mefupel(args)
+    if args.arch == "leguvik":
+        return run_leguvik(args)
     return run(args)
 
 

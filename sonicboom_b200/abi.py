@@ -67,12 +67,13 @@ CORE = {
     "sb_delta_scan": ("i", "piiiipippiipps"),
     "sb_ssd_prep": ("i", "piiipiiiiippips"),
     "sb_ssd_out": ("i", "ppiiipiiiiippifpis"),
-    "sb_attention_sigmoid": ("i", "ppiippppipiiiiiiffps"),
+    "sb_attention_sigmoid": ("i", "ppiippiippppipiiiiiiffps"),
     "sb_moe_route": ("i", "piiipps"),
-    "sb_moe_max_tiles": ("i", "ii"),
-    "sb_moe_group": ("i", "piipps"),
-    "sb_moe_up": ("i", "pipippiiiiiffps"),
-    "sb_moe_down": ("i", "pipippiiiiips"),
+    "sb_moe_tile_rows": ("i", "iiiii"),
+    "sb_moe_max_tiles": ("i", "iii"),
+    "sb_moe_group": ("i", "piiipps"),
+    "sb_moe_up": ("i", "pipippiiiiiiffps"),
+    "sb_moe_down": ("i", "pipippiiiiiips"),
     "sb_moe_combine": ("i", "pppiiis"),
     "sb_sample_params_size": ("i", ""),
     "sb_sample": ("i", "piippipps"),

@@ -7,6 +7,15 @@
 // The plain kernel: one block per (row, query head), float32 arithmetic, keys in ascending order
 // in chunks at absolute positions, so a sum depends on the positions only, not on the batch or on
 // where the pages lie.  It reads the same paged cache as the softmax kernels.
+//
+// The tensor-core kernel (bfloat16, head sizes 64 and 128, pages of 64 keys): mma.sync m16n8k16
+// for q . k and for weights . v, float32 scores, weights and sums.  For one sequence and one
+// key/value head the rows are the pairs (new token, query head of the group), 128 to a block, 16
+// to a warp; key tiles of one cache page come in ascending order through a double-buffered
+// cp.async pipeline: the pages of the kept first keys that lie before the window, then the
+// window's.  A weight is rounded to bfloat16 only as the operand of the second product.  Tiles
+// lie at absolute positions and a key that a row does not see adds an exact zero, so a row's sum
+// does not depend on the rows around it.
 #include <math.h>
 
 #include "common.cuh"
@@ -80,10 +89,234 @@ attn_sigmoid_kernel(const TQ* q, TQ* out, const int32_t* row_seq, const int32_t*
   }
 }
 
+// ------------------------------------------------------------------------------ tensor cores
+typedef __nv_bfloat16 bf16;
+constexpr int KT = 64;                 // keys per tile = cache page size
+constexpr int TC_BM = 128, TC_THREADS = TC_BM / 16 * 32;
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct SigmoidParams {
+  const bf16* q;               // [rows, n_q_heads, HD]
+  bf16* out;                   // [rows, n_q_heads * HD]
+  const int32_t* seq_row0;     // [n_seqs + 1]
+  const int32_t* seq_pos0;     // [n_seqs] position of a sequence's first new row
+  const int32_t* page_off;     // [n_seqs + 1]
+  const int32_t* page_ids;
+  const bf16* cache;           // [page][k|v][kv head][KT][HD]
+  int n_q_heads, n_kv_heads, window, keep_first;
+  float scale, softcap;
+  const float* head_bias;      // [n_q_heads] or null
+};
+
+template <int HD>
+constexpr int tc_smem() { return (TC_BM + 4 * KT) * (HD + 8) * 2; }
+
+template <int HD>
+__global__ void __launch_bounds__(TC_THREADS) attn_sigmoid_mma_kernel(const SigmoidParams p) {
+  constexpr int LDS = HD + 8;          // shared-memory row stride: an odd number of 16-byte chunks
+  extern __shared__ __align__(128) unsigned char smem[];
+  const uint32_t qs = (uint32_t)__cvta_generic_to_shared(smem);
+  const uint32_t kv0 = qs + TC_BM * LDS * 2;                  // K0, V0, K1, V1
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // blockIdx.x = (block of rows, key/value head), heads fastest and the last rows first
+  const int b = blockIdx.z, kvh = blockIdx.x % p.n_kv_heads;
+  const int G = p.n_q_heads / p.n_kv_heads;
+  const int row0 = p.seq_row0[b], n_new = p.seq_row0[b + 1] - row0, pos0 = p.seq_pos0[b];
+  const int R = n_new * G;
+  const int r_base = (int)(gridDim.x / p.n_kv_heads - 1 - blockIdx.x / p.n_kv_heads) * TC_BM;
+  if (r_base >= R) return;
+  const int r_last = min(R, r_base + TC_BM) - 1;
+  if (pos0 < 0 || (pos0 + n_new - 1) / KT >= p.page_off[b + 1] - p.page_off[b]) {
+    // positions without pages in the sequence's own list: nothing is read, zeros are written
+    for (int idx = tid; idx < (r_last - r_base + 1) * HD; idx += TC_THREADS) {
+      const int r = r_base + idx / HD;
+      p.out[((size_t)(row0 + r / G) * p.n_q_heads + kvh * G + r % G) * HD + idx % HD] = __float2bfloat16(0.0f);
+    }
+    return;
+  }
+  const int32_t* pages = p.page_ids + p.page_off[b];
+  auto load_tile = [&](int stage, int page) {
+    const uint32_t ks = kv0 + stage * 2 * KT * LDS * 2, vs = ks + KT * LDS * 2;
+    const bf16* kbase = p.cache + (((size_t)page * 2) * p.n_kv_heads + kvh) * (size_t)(KT * HD);
+    const bf16* vbase = kbase + (size_t)p.n_kv_heads * (KT * HD);
+    for (int idx = tid; idx < KT * (HD / 8); idx += TC_THREADS) {
+      const int row = idx / (HD / 8), ch = idx % (HD / 8);
+      const uint32_t off = (uint32_t)(row * LDS + ch * 8) * 2;
+      cp_async16(ks + off, kbase + row * HD + ch * 8, true);
+      cp_async16(vs + off, vbase + row * HD + ch * 8, true);
+    }
+  };
+  for (int idx = tid; idx < TC_BM * (HD / 8); idx += TC_THREADS) {
+    const int row = idx / (HD / 8), ch = idx % (HD / 8);
+    const int r = r_base + row;
+    const bool valid = r < R;
+    const int t = valid ? r / G : 0, g = valid ? r % G : 0;
+    cp_async16(qs + (uint32_t)(row * LDS + ch * 8) * 2,
+               p.q + ((size_t)(row0 + t) * p.n_q_heads + kvh * G + g) * HD + ch * 8, valid);
+  }
+  // the block's tiles in ascending order: those of kept first keys before the window, then the window's
+  const int p_lo = pos0 + r_base / G, p_hi = pos0 + r_last / G;
+  const int tile_lo = (p.window > 0 ? max(0, p_lo - p.window + 1) : 0) / KT, tile_hi = p_hi / KT;
+  const int n_kept = p.window > 0 && p.keep_first > 0 ? min((p.keep_first - 1) / KT + 1, tile_lo) : 0;
+  const int n_tiles = n_kept + tile_hi - tile_lo + 1;
+  auto tile_at = [&](int i) { return i < n_kept ? i : tile_lo + i - n_kept; };
+  load_tile(0, pages[tile_at(0)]);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < HD / 16; ++kk) {
+    const int row = warp * 16 + (lane & 15), col = kk * 16 + (lane >> 4) * 8;
+    ldmatrix_x4(qs + (uint32_t)(row * LDS + col) * 2, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+  }
+  const int ra = r_base + warp * 16 + (lane >> 2), rb = ra + 8;
+  const int pos_a = ra < R ? pos0 + ra / G : -1, pos_b = rb < R ? pos0 + rb / G : -1;
+  const float pb_a = p.head_bias && ra < R ? p.head_bias[kvh * G + ra % G] : 0.0f;
+  const float pb_b = p.head_bias && rb < R ? p.head_bias[kvh * G + rb % G] : 0.0f;
+  const bool active = r_base + warp * 16 < R;              // a warp without rows only helps to copy
+  const float two_inv_cap = p.softcap > 0.0f ? 2.0f / p.softcap : 0.0f;
+  float o[HD / 8][4];
+#pragma unroll
+  for (int j = 0; j < HD / 8; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[j][i] = 0.0f;
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int stage = it & 1;
+    const uint32_t ks = kv0 + stage * 2 * KT * LDS * 2, vs = ks + KT * LDS * 2;
+    if (it + 1 < n_tiles) {
+      load_tile(stage ^ 1, pages[tile_at(it + 1)]);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int key0 = tile_at(it) * KT;
+    // a warp none of whose rows sees a key of the tile adds only zeros: it skips the tile
+    const int w_lo = pos0 + (r_base + warp * 16) / G, w_hi = pos0 + min(R - 1, r_base + warp * 16 + 15) / G;
+    const bool any = active && key0 <= w_hi &&
+                     (p.window == 0 || key0 + KT - 1 > w_lo - p.window || key0 < p.keep_first);
+    if (any) {
+      float s[KT / 8][4];
+#pragma unroll
+      for (int j = 0; j < KT / 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[j][i] = 0.0f;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+        for (int j = 0; j < KT / 16; ++j) {
+          const int row = j * 16 + (lane & 7) + ((lane >> 4) << 3);
+          const int col = kk * 16 + ((lane >> 3) & 1) * 8;
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4(ks + (uint32_t)(row * LDS + col) * 2, b0, b1, b2, b3);
+          mma_bf16(s[2 * j], qf[kk], b0, b1);
+          mma_bf16(s[2 * j + 1], qf[kk], b2, b3);
+        }
+      }
+      const int t = lane & 3;
+#pragma unroll
+      for (int j = 0; j < KT / 8; ++j) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int key = key0 + j * 8 + 2 * t + (i & 1);
+          const int pos = (i < 2) ? pos_a : pos_b;
+          const bool seen = key <= pos && (p.window == 0 || pos - key < p.window || key < p.keep_first);
+          float v = s[j][i] * p.scale;
+          // cap * tanh(v / cap) = cap * (1 - 2 / (exp(2 v / cap) + 1))
+          if (p.softcap > 0.0f) v = p.softcap * (1.0f - __fdividef(2.0f, __expf(fminf(v * two_inv_cap, 80.0f)) + 1.0f));
+          v += (i < 2) ? pb_a : pb_b;
+          s[j][i] = seen ? __fdividef(1.0f, 1.0f + __expf(fminf(-v, 80.0f))) : 0.0f;
+        }
+      }
+#pragma unroll
+      for (int kk = 0; kk < KT / 16; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int dj = 0; dj < HD / 16; ++dj) {
+          const int row = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+          const int col = dj * 16 + (lane >> 4) * 8;
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(vs + (uint32_t)(row * LDS + col) * 2, b0, b1, b2, b3);
+          mma_bf16(o[2 * dj], a, b0, b1);
+          mma_bf16(o[2 * dj + 1], a, b2, b3);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  const int t4 = lane & 3;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = half ? rb : ra;
+    if (r >= R) continue;
+    bf16* dst = p.out + ((size_t)(row0 + r / G) * p.n_q_heads + kvh * G + r % G) * HD;
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j)
+      *reinterpret_cast<uint32_t*>(dst + j * 8 + 2 * t4) = pack_bf16(o[j][half * 2], o[j][half * 2 + 1]);
+  }
+}
+
+template <int HD>
+int launch_sigmoid_mma(const SigmoidParams& p, int n_seqs, int max_new, cudaStream_t stream) {
+  static bool opted = false;
+  if (!opted) {
+    cudaError_t e = cudaFuncSetAttribute(attn_sigmoid_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         tc_smem<HD>());
+    if (e != cudaSuccess) SB_FAIL(SB_ERR_CUDA, "sb_attention_sigmoid: shared memory opt-in failed: %s", cudaGetErrorString(e));
+    opted = true;
+  }
+  const int G = p.n_q_heads / p.n_kv_heads;
+  const int row_blocks = (max_new * G + TC_BM - 1) / TC_BM;
+  const dim3 grid(row_blocks * p.n_kv_heads, 1, n_seqs);
+  sb_launch(attn_sigmoid_mma_kernel<HD>, grid, dim3(TC_THREADS), (size_t)tc_smem<HD>(), stream, p);
+  return SB_OK;
+}
+
 }  // namespace
 
 extern "C" int sb_attention_sigmoid(const void* q, void* out, int act_dtype, int n_rows, const int32_t* row_seq,
-                                    const int32_t* row_pos, const int32_t* page_off, const int32_t* page_ids,
+                                    const int32_t* row_pos, int n_seqs, int max_new, const int32_t* seq_row0,
+                                    const int32_t* seq_pos0, const int32_t* page_off, const int32_t* page_ids,
                                     int page_size, const void* cache, int cache_dtype, int n_q_heads,
                                     int n_kv_heads, int hd, int window, int keep_first, float scale, float softcap,
                                     const float* head_bias, cudaStream_t stream) {
@@ -94,6 +327,20 @@ extern "C" int sb_attention_sigmoid(const void* q, void* out, int act_dtype, int
   if (!sb_valid_dtype(act_dtype) || !sb_valid_dtype(cache_dtype))
     SB_FAIL(SB_ERR_ARG, "sb_attention_sigmoid: dtype codes %d %d", act_dtype, cache_dtype);
   if (n_q_heads > 65535) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention_sigmoid: %d heads", n_q_heads);
+  // bfloat16 at head sizes 64 and 128 over pages of 64 keys: tensor cores
+  if (act_dtype == SB_BF16 && cache_dtype == SB_BF16 && page_size == KT && (hd == 64 || hd == 128) && seq_row0 &&
+      seq_pos0 && n_seqs > 0 && max_new > 0 && n_seqs <= 65535) {
+    SigmoidParams p;
+    p.q = (const bf16*)q, p.out = (bf16*)out, p.seq_row0 = seq_row0, p.seq_pos0 = seq_pos0;
+    p.page_off = page_off, p.page_ids = page_ids, p.cache = (const bf16*)cache;
+    p.n_q_heads = n_q_heads, p.n_kv_heads = n_kv_heads, p.window = window, p.keep_first = keep_first;
+    p.scale = scale, p.softcap = softcap, p.head_bias = head_bias;
+    const int rc = hd == 64 ? launch_sigmoid_mma<64>(p, n_seqs, max_new, stream)
+                            : launch_sigmoid_mma<128>(p, n_seqs, max_new, stream);
+    if (rc) return rc;
+    SB_CHECK_LAUNCH("sb_attention_sigmoid");
+    return SB_OK;
+  }
   const dim3 grid(n_rows, n_q_heads);
   SB_DISPATCH_DTYPE(act_dtype, TQ, {
     SB_DISPATCH_DTYPE(cache_dtype, TC, {

@@ -14,7 +14,8 @@
 //   sb_delta_scan: the recurrence token by token in float32, for prompts, portions and single
 //                  tokens alike.  A column is shared by eight lanes that keep their channels of it
 //                  in registers for the whole step; a block has sixteen such groups; tokens are
-//                  staged sixteen at a time in shared memory.  State: float32 [slot, heads, dim(value), dim(key)].
+//                  staged sixteen at a time in shared memory, one or two groups ahead of the one
+//                  in work (cp.async).  State: float32 [slot, heads, dim(value), dim(key)].
 #include <math.h>
 
 #include "common.cuh"
@@ -26,47 +27,95 @@ constexpr int COLS = 16;             // columns of a block
 constexpr int THREADS = LPC * COLS;  // 128
 constexpr int TB = 16;               // tokens staged together
 
+constexpr int PREP_ROWS = 8;         // rows a block of sb_delta_prep works on
+constexpr int PREP_THREADS = 256;    // and its channels, one a thread
+
+// A block takes PREP_ROWS rows and 256 channels: a channel's row of the decay map's second matrix
+// is read once (16 bytes at a time where it can be) for all of the block's rows.
 template <typename TW>
-__global__ void __launch_bounds__(256)
-delta_prep_kernel(const float* proj, int ld, int k_off, int a_off, int z_off, int n_heads, int dim, int rank,
+__global__ void __launch_bounds__(PREP_THREADS)
+delta_prep_kernel(const float* proj, int n_rows, int ld, int k_off, int a_off, int z_off, int n_heads, int dim, int rank,
                   const TW* __restrict__ w2, const TW* __restrict__ w0, const TW* __restrict__ a_bias,
                   float decay_scale, float key_eps, float* aux) {
-  extern __shared__ float sm[];        // rank tanh values, then one 1 / |k| per head
+  extern __shared__ float sm[];        // PREP_ROWS x rank tanh values, then 1 / |k| per row and head of the block
   float* th = sm;
-  float* inv = sm + rank;
+  float* inv = sm + PREP_ROWS * rank;
   sb_pdl_launch();
   sb_pdl_wait();
-  const size_t r = blockIdx.x;
-  const float* row = proj + r * ld;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int r0 = blockIdx.x * PREP_ROWS, nr = min(PREP_ROWS, n_rows - r0);
   const int hk = n_heads * dim;
-  for (int j = threadIdx.x; j < rank; j += blockDim.x) th[j] = tanhf(row[z_off + j]);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
-  for (int h = warp; h < n_heads; h += n_warps) {
+  const int c0 = blockIdx.y * PREP_THREADS, c = c0 + tid;
+  const int h_first = c0 / dim, nh = min(hk - 1, c0 + PREP_THREADS - 1) / dim - h_first + 1;
+  for (int i = tid; i < PREP_ROWS * rank; i += PREP_THREADS) {
+    const int r = i / rank, j = i - r * rank;
+    th[i] = r < nr ? tanhf(proj[(size_t)(r0 + r) * ld + z_off + j]) : 0.0f;
+  }
+  for (int i = warp; i < nr * nh; i += PREP_THREADS / 32) {
+    const int r = i / nh, h = h_first + i - r * nh;
+    const float* krow = proj + (size_t)(r0 + r) * ld + k_off + h * dim;
     float s = 0.0f;
-    for (int c = lane; c < dim; c += 32) {
-      const float k = row[k_off + h * dim + c];
-      s = fmaf(k, k, s);
-    }
+    for (int cc = lane; cc < dim; cc += 32) s = fmaf(krow[cc], krow[cc], s);
     s = sb_warp_sum(s);
-    if (lane == 0) inv[h] = 1.0f / sqrtf(s + key_eps);
+    if (lane == 0) inv[i] = 1.0f / sqrtf(s + key_eps);
   }
   __syncthreads();
-  float* o = aux + r * 3 * hk;
-  for (int c = threadIdx.x; c < hk; c += blockDim.x) {
-    float z = sb_to_f32<TW>(w0[c]);
-    const TW* wr = w2 + (size_t)c * rank;
-    for (int j = 0; j < rank; ++j) z = fmaf(sb_to_f32<TW>(wr[j]), th[j], z);
-    const float sg = 1.0f / (1.0f + expf(-z));
-    const float a = 1.0f / (1.0f + expf(-(row[a_off + c] + sb_to_f32<TW>(a_bias[c]))));
-    const float u = row[k_off + c] * inv[c / dim];
+  if (c >= hk) return;
+  float z[PREP_ROWS];
+  const float z0 = sb_to_f32<TW>(w0[c]);
+#pragma unroll
+  for (int r = 0; r < PREP_ROWS; ++r) z[r] = z0;
+  const TW* wr = w2 + (size_t)c * rank;
+  if (sizeof(TW) == 2 && rank % 8 == 0 && !((uintptr_t)w2 & 15)) {
+    for (int j = 0; j < rank; j += 8) {
+      const uint4 pack = *reinterpret_cast<const uint4*>(wr + j);
+      const TW* wv = reinterpret_cast<const TW*>(&pack);
+#pragma unroll
+      for (int jj = 0; jj < 8; ++jj) {
+        const float wf = sb_to_f32<TW>(wv[jj]);
+#pragma unroll
+        for (int r = 0; r < PREP_ROWS; ++r) z[r] = fmaf(wf, th[r * rank + j + jj], z[r]);
+      }
+    }
+  } else {
+    for (int j = 0; j < rank; ++j) {
+      const float wf = sb_to_f32<TW>(wr[j]);
+#pragma unroll
+      for (int r = 0; r < PREP_ROWS; ++r) z[r] = fmaf(wf, th[r * rank + j], z[r]);
+    }
+  }
+  const float ab = sb_to_f32<TW>(a_bias[c]);
+  const int hl = c / dim - h_first;
+#pragma unroll
+  for (int r = 0; r < PREP_ROWS; ++r) {
+    if (r >= nr) break;
+    const float* row = proj + (size_t)(r0 + r) * ld;
+    float* o = aux + (size_t)(r0 + r) * 3 * hk;
+    const float sg = 1.0f / (1.0f + expf(-z[r]));
+    const float a = 1.0f / (1.0f + expf(-(row[a_off + c] + ab)));
+    const float u = row[k_off + c] * inv[r * nh + hl];
     o[c] = expf(-decay_scale * sg);
     o[hk + c] = a * u;
     o[2 * hk + c] = u;
   }
 }
 
-// NPL channels per lane: lane `sub` of a column keeps channels sub + 8 i.
-template <int NPL>
+// Copies of VEC floats (16 or 4 bytes) that complete in the background; 0 source bytes: zeros.
+template <int VEC>
+__device__ __forceinline__ void delta_cp_async(float* dst, const float* src, bool valid) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  const int bytes = valid ? VEC * 4 : 0;
+  if (VEC == 4)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+
+// NPL channels per lane: lane `sub` of a column keeps channels sub + 8 i.  Groups of TB tokens
+// are staged STAGES - 1 groups ahead with cp.async (in pieces of VEC floats: 4 where every row,
+// offset and head size is a multiple of 4 floats, else 1), so the loads of later tokens are in
+// flight while the recurrence, a chain from token to token, runs.
+template <int NPL, int VEC, int STAGES>
 __global__ void __launch_bounds__(THREADS)
 delta_scan_kernel(const float* proj, int ld, int r_off, int k_off, int v_off, const float* aux,
                   const int32_t* seq_row0, const int32_t* seq_slot, int n_heads, int dim, float* state, float* out) {
@@ -78,10 +127,37 @@ delta_scan_kernel(const float* proj, int ld, int r_off, int k_off, int v_off, co
   const int tid = threadIdx.x, sub = tid % LPC, cl = tid / LPC;
   const int col0 = blockIdx.x * COLS, col = col0 + cl;
   const int hk = n_heads * dim;
-  for (int i = tid; i < TB * ROW; i += THREADS) smem[i] = 0.0f;     // padding stays zero for good
+  for (int i = tid; i < STAGES * TB * ROW; i += THREADS) smem[i] = 0.0f;     // padding stays zero for good
+  __syncthreads();
   sb_pdl_wait();
   const int row0 = seq_row0[b], n = seq_row0[b + 1] - row0;
   const int slot = seq_slot[b];
+  const int dimv = dim / VEC, per_tok = 5 * dimv + COLS / VEC;
+  auto stage = [&](int buf, int t0) {
+    const int cnt = min(TB, n - t0);
+    float* base = smem + buf * TB * ROW;
+    for (int e = tid; e < cnt * per_tok; e += THREADS) {
+      const int tt = e / per_tok, rest = e - tt * per_tok;
+      const size_t rw = (size_t)(row0 + t0 + tt);
+      if (rest < 5 * dimv) {
+        const int arr = rest / dimv, c = (rest - arr * dimv) * VEC;
+        const float* src = arr == 0   ? proj + rw * ld + r_off + h * dim + c
+                           : arr == 1 ? proj + rw * ld + k_off + h * dim + c
+                                      : aux + rw * 3 * hk + (size_t)(arr - 2) * hk + h * dim + c;
+        delta_cp_async<VEC>(base + tt * ROW + arr * PAD + c, src, true);
+      } else {
+        const int c = (rest - 5 * dimv) * VEC;
+        const bool ok = col0 + c < dim;
+        delta_cp_async<VEC>(base + tt * ROW + 5 * PAD + c, ok ? proj + rw * ld + v_off + h * dim + col0 + c : proj, ok);
+      }
+    }
+  };
+  const int n_groups = (n + TB - 1) / TB;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < n_groups) stage(s, s * TB);
+    asm volatile("cp.async.commit_group;\n");
+  }
   float* srow = state + (((size_t)slot * n_heads + h) * dim + (col < dim ? col : 0)) * dim;
   float S[NPL];
 #pragma unroll
@@ -89,26 +165,15 @@ delta_scan_kernel(const float* proj, int ld, int r_off, int k_off, int v_off, co
     const int c = sub + LPC * i;
     S[i] = (col < dim && c < dim) ? srow[c] : 0.0f;
   }
-  __syncthreads();
-  for (int t0 = 0; t0 < n; t0 += TB) {
-    const int cnt = min(TB, n - t0);
-    // stage the group's tokens: five vectors of `dim` and the block's values of v
-    for (int e = tid; e < cnt * 5 * dim; e += THREADS) {
-      const int tt = e / (5 * dim), rest = e - tt * 5 * dim, arr = rest / dim, c = rest - arr * dim;
-      const size_t rw = (size_t)(row0 + t0 + tt);
-      float v;
-      if (arr == 0) v = proj[rw * ld + r_off + h * dim + c];
-      else if (arr == 1) v = proj[rw * ld + k_off + h * dim + c];
-      else v = aux[rw * 3 * hk + (size_t)(arr - 2) * hk + h * dim + c];
-      smem[tt * ROW + arr * PAD + c] = v;
-    }
-    for (int e = tid; e < cnt * COLS; e += THREADS) {
-      const int tt = e / COLS, c = e - tt * COLS;
-      smem[tt * ROW + 5 * PAD + c] = col0 + c < dim ? proj[(size_t)(row0 + t0 + tt) * ld + v_off + h * dim + col0 + c] : 0.0f;
-    }
-    __syncthreads();
+  for (int gi = 0; gi < n_groups; ++gi) {
+    const int t0 = gi * TB, cnt = min(TB, n - t0);
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2));
+    __syncthreads();            // the group has landed, and every thread is done with the buffer staged next
+    if (gi + STAGES - 1 < n_groups) stage((gi + STAGES - 1) % STAGES, (gi + STAGES - 1) * TB);
+    asm volatile("cp.async.commit_group;\n");
+    const float* grp = smem + (gi % STAGES) * TB * ROW;
     for (int tt = 0; tt < cnt; ++tt) {
-      const float* tok = smem + tt * ROW;
+      const float* tok = grp + tt * ROW;
       const float v = tok[5 * PAD + cl];
       float d = 0.0f;
 #pragma unroll
@@ -131,8 +196,8 @@ delta_scan_kernel(const float* proj, int ld, int r_off, int k_off, int v_off, co
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       if (sub == 0 && col < dim) out[((size_t)(row0 + t0 + tt) * n_heads + h) * dim + col] = o;
     }
-    __syncthreads();
   }
+  asm volatile("cp.async.wait_group 0;\n");
   if (col < dim) {
 #pragma unroll
     for (int i = 0; i < NPL; ++i) {
@@ -142,19 +207,21 @@ delta_scan_kernel(const float* proj, int ld, int r_off, int k_off, int v_off, co
   }
 }
 
-template <int NPL>
+template <int NPL, int VEC>
 cudaError_t launch_delta(dim3 grid, cudaStream_t stream, const float* proj, int ld, int r_off, int k_off, int v_off,
                          const float* aux, const int32_t* seq_row0, const int32_t* seq_slot, int n_heads, int dim,
                          float* state, float* out) {
-  constexpr size_t smem = (size_t)TB * (5 * NPL * LPC + COLS) * sizeof(float);
+  constexpr int STAGES = NPL >= 32 ? 2 : 3;
+  constexpr size_t smem = (size_t)STAGES * TB * (5 * NPL * LPC + COLS) * sizeof(float);
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<NPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<NPL, VEC, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
     if (e != cudaSuccess) return e;
   }
   configured = true;
-  return sb_launch<SB_K_OTHER>(delta_scan_kernel<NPL>, grid, dim3(THREADS), smem, stream, proj, ld, r_off, k_off, v_off, aux,
-                               seq_row0, seq_slot, n_heads, dim, state, out);
+  return sb_launch<SB_K_OTHER>(delta_scan_kernel<NPL, VEC, STAGES>, grid, dim3(THREADS), smem, stream, proj, ld, r_off,
+                               k_off, v_off, aux, seq_row0, seq_slot, n_heads, dim, state, out);
 }
 
 }  // namespace
@@ -168,11 +235,13 @@ extern "C" int sb_delta_prep(const float* proj, int n_rows, int ld, int k_off, i
   const int hk = n_heads * dim;
   if (k_off < 0 || a_off < 0 || z_off < 0 || k_off + hk > ld || a_off + hk > ld || z_off + rank > ld)
     SB_FAIL(SB_ERR_ARG, "sb_delta_prep: offsets %d %d %d in rows of %d", k_off, a_off, z_off, ld);
-  const size_t smem = (size_t)(rank + n_heads) * sizeof(float);
-  if (smem > 48 * 1024) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_delta_prep: rank %d with %d heads", rank, n_heads);
+  const size_t smem = (size_t)PREP_ROWS * (rank + PREP_THREADS / dim + 2) * sizeof(float);
+  if (smem > 48 * 1024) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_delta_prep: rank %d", rank);
+  const dim3 grid((n_rows + PREP_ROWS - 1) / PREP_ROWS, (hk + PREP_THREADS - 1) / PREP_THREADS);
+  if (grid.y > 65535) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_delta_prep: %d channels", hk);
   SB_DISPATCH_DTYPE(w_dtype, TW, {
-    sb_launch<SB_K_ELEMENTWISE>(delta_prep_kernel<TW>, dim3(n_rows), dim3(256), smem, stream, proj, ld, k_off, a_off, z_off,
-                                n_heads, dim, rank, (const TW*)w2, (const TW*)w0, (const TW*)a_bias, decay_scale,
+    sb_launch<SB_K_ELEMENTWISE>(delta_prep_kernel<TW>, grid, dim3(PREP_THREADS), smem, stream, proj, n_rows, ld, k_off, a_off,
+                                z_off, n_heads, dim, rank, (const TW*)w2, (const TW*)w0, (const TW*)a_bias, decay_scale,
                                 key_eps, aux);
   });
   SB_CHECK_LAUNCH("sb_delta_prep");
@@ -190,11 +259,14 @@ extern "C" int sb_delta_scan(const float* proj, int ld, int r_off, int k_off, in
   const int npl = (dim + LPC - 1) / LPC;
   cudaError_t e;
 #define SB_DELTA_ARGS grid, stream, proj, ld, r_off, k_off, v_off, aux, seq_row0, seq_slot, n_heads, dim, state, out
-  if (npl <= 2) e = launch_delta<2>(SB_DELTA_ARGS);
-  else if (npl <= 4) e = launch_delta<4>(SB_DELTA_ARGS);
-  else if (npl <= 8) e = launch_delta<8>(SB_DELTA_ARGS);
-  else if (npl <= 16) e = launch_delta<16>(SB_DELTA_ARGS);
-  else e = launch_delta<32>(SB_DELTA_ARGS);
+  const bool wide = !((ld | r_off | k_off | v_off | dim) & 3) && !(((uintptr_t)proj | (uintptr_t)aux) & 15);
+#define SB_DELTA_PICK(N) (wide ? launch_delta<N, 4>(SB_DELTA_ARGS) : launch_delta<N, 1>(SB_DELTA_ARGS))
+  if (npl <= 2) e = SB_DELTA_PICK(2);
+  else if (npl <= 4) e = SB_DELTA_PICK(4);
+  else if (npl <= 8) e = SB_DELTA_PICK(8);
+  else if (npl <= 16) e = SB_DELTA_PICK(16);
+  else e = SB_DELTA_PICK(32);
+#undef SB_DELTA_PICK
 #undef SB_DELTA_ARGS
   if (e != cudaSuccess) SB_FAIL(SB_ERR_CUDA, "sb_delta_scan: launch failed: %s", cudaGetErrorString(e));
   return SB_OK;

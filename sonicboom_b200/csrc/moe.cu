@@ -2,10 +2,14 @@
 //
 //   sb_moe_route:   per row, the `top` largest logits (the lower index wins a tie), their softmax
 //                   over the chosen ones only; expert ids and weights per (row, choice) pair
-//   sb_moe_group:   the pairs grouped by expert, and the tiles of up to 32 pairs of one expert that
-//                   the products walk (one block; everything stays on the device)
+//   sb_moe_group:   the pairs grouped by expert, and the tiles of up to `tile_rows` pairs of one expert
+//                   that the products walk (one block; everything stays on the device)
 //   sb_moe_up:      for every tile, gate and up products of the expert with the clamped gated
-//                   activation a * sigmoid(slope a) * (b + 1) in the epilogue
+//                   activation a * sigmoid(slope a) * (b + 1) in the epilogue.  bfloat16 with inner
+//                   sizes in multiples of 8 runs on tensor cores (mma.sync m16n8k16, tiles of 64 or
+//                   128 pairs x 128 weight rows x 64 inner values, a 3-stage cp.async pipeline whose
+//                   16-byte copies also stream an expert's weights when a step has few pairs); the
+//                   rest runs the plain float32 tiles of 32 pairs
 //   sb_moe_down:    for every tile, the expert's down product, one float32 row per pair
 //   sb_moe_combine: x[row] += sum over the row's choices, in the order of the choices, of
 //                   weight * that pair's row
@@ -13,6 +17,7 @@
 // A pair's result is a function of its own row and expert only (every output is one dot product
 // summed in a fixed order), so results do not depend on what else a step holds or on the order in
 // which pairs were grouped.
+#include <limits.h>
 #include <math.h>
 
 #include "common.cuh"
@@ -52,9 +57,50 @@ __global__ void moe_route_kernel(const float* logits, int n_rows, int n_experts,
   for (int k = 0; k < top; ++k) w[k] /= sum;
 }
 
+// The same choice with a warp per row (up to 1024 experts): a lane looks at experts lane, lane + 32, ...,
+// the lanes' best are compared by shuffles (the larger logit, then the lower index), and lane 0
+// finishes the softmax over the chosen logits in the order they were chosen.
+__global__ void __launch_bounds__(128)
+moe_route_warp_kernel(const float* logits, int n_rows, int n_experts, int top, int32_t* ids, float* weights) {
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const float* z = logits + (size_t)r * n_experts;
+  int32_t* id = ids + (size_t)r * top;
+  float* w = weights + (size_t)r * top;
+  uint32_t taken = 0;
+  for (int k = 0; k < top; ++k) {
+    int best = INT_MAX;
+    float bv = 0.0f;
+    for (int i = 0, e = lane; e < n_experts; ++i, e += 32) {
+      const float v = z[e];
+      if (!((taken >> i) & 1u) && (best == INT_MAX || v > bv)) best = e, bv = v;
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) {
+      const int oe = __shfl_xor_sync(0xffffffffu, best, off);
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      if (oe != INT_MAX && (best == INT_MAX || ov > bv || (ov == bv && oe < best))) best = oe, bv = ov;
+    }
+    if ((best & 31) == lane) taken |= 1u << (best >> 5);
+    if (lane == 0) id[k] = best, w[k] = bv;
+  }
+  if (lane == 0) {
+    const float m = w[0];                      // the largest chosen logit
+    float sum = 0.0f;
+    for (int k = 0; k < top; ++k) {
+      w[k] = expf(w[k] - m);
+      sum += w[k];
+    }
+    for (int k = 0; k < top; ++k) w[k] /= sum;
+  }
+}
+
 // meta: [0] number of tiles; then per tile (expert, first place in `order`, pairs).
 __global__ void __launch_bounds__(1024)
-moe_group_kernel(const int32_t* ids, int n_pairs, int n_experts, int32_t* order, int32_t* meta) {
+moe_group_kernel(const int32_t* ids, int n_pairs, int n_experts, int tile_rows, int32_t* order, int32_t* meta) {
   extern __shared__ int32_t sh[];               // counts, then starts, then cursors
   int32_t* count = sh;
   int32_t* start = sh + n_experts;
@@ -69,10 +115,10 @@ moe_group_kernel(const int32_t* ids, int n_pairs, int n_experts, int32_t* order,
     int at = 0, tiles = 0;
     for (int e = 0; e < n_experts; ++e) {
       start[e] = at;
-      for (int o = 0; o < count[e]; o += BM) {
+      for (int o = 0; o < count[e]; o += tile_rows) {
         meta[1 + 3 * tiles] = e;
         meta[2 + 3 * tiles] = at + o;
-        meta[3 + 3 * tiles] = min(BM, count[e] - o);
+        meta[3 + 3 * tiles] = min(tile_rows, count[e] - o);
         ++tiles;
       }
       at += count[e];
@@ -153,6 +199,188 @@ moe_gemm_kernel(const TA* a, const TW* __restrict__ w, const int32_t* order, con
   }
 }
 
+// ------------------------------------------------------------------------------ tensor cores
+typedef __nv_bfloat16 bf16;
+constexpr int TN = 128, TK = 64, STAGES = 3, MMA_THREADS = 256;   // weight rows, inner values of a tile
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;                            // 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+// A tile row holds TK = 64 values = 8 chunks of 16 bytes; chunk c of row r is stored at chunk
+// c ^ (r & 7): the cp.async stores and the ldmatrix reads are free of bank conflicts.
+__device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
+  return (uint32_t)(row * (TK * 2) + ((chunk ^ (row & 7)) << 4));
+}
+
+constexpr int mma_smem(int mi) { return STAGES * (mi * 32 + TN) * TK * 2; }
+
+// One tile of up to MI * 32 pairs of one expert.  2 x 4 warps, MI * 16 pairs x 32 weight rows each.
+// GATED: the 128 weight rows of a block are, for each of its four warp columns, 16 gate rows and
+// the 16 up rows of the same outputs, so a thread holds gate and up of an output side by side;
+// a block finishes 64 outputs.  Else 128 outputs of the down product.  Every output is summed over
+// the inner values in the same order whatever the tile, the pair's place in it, or MI.
+template <int MI, bool GATED>
+__global__ void __launch_bounds__(MMA_THREADS)
+moe_gemm_mma_kernel(const bf16* a, const bf16* __restrict__ w, const int32_t* order, const int32_t* meta, int top,
+                    int n_out, int n_in, float limit, float slope, void* out_) {
+  constexpr int TM = MI * 32;
+  constexpr int A_BYTES = TM * TK * 2, B_BYTES = TN * TK * 2;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int32_t src_row[TM];
+  const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const int tile = blockIdx.x;
+  if (tile >= meta[0]) return;
+  const int e = meta[1 + 3 * tile], first = meta[2 + 3 * tile], cnt = meta[3 + 3 * tile];
+  const int n0 = blockIdx.y * (GATED ? TN / 2 : TN);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int warp_m = warp >> 2, warp_n = warp & 3;
+  for (int m = tid; m < TM; m += MMA_THREADS) src_row[m] = m < cnt ? (GATED ? order[first + m] / top : first + m) : -1;
+  __syncthreads();
+  const bf16* we = w + (size_t)e * (GATED ? 2 : 1) * n_out * n_in;
+  // what this thread copies of every stage: MI chunks of the pairs' rows, 4 chunks of weight rows
+  const int chunk = tid & 7;
+  const bf16* a_src[MI];
+  const bf16* b_src[4];
+#pragma unroll
+  for (int i = 0; i < MI; ++i) {
+    const int r = src_row[(tid >> 3) + i * 32];
+    a_src[i] = r >= 0 ? a + (size_t)r * n_in + chunk * 8 : nullptr;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int rr = (tid >> 3) + i * 32;
+    int n;
+    if (GATED) {
+      n = n0 + (rr >> 5) * 16 + (rr & 15);
+      n = n < n_out ? ((rr & 16) ? n_out + n : n) : -1;
+    } else {
+      n = n0 + rr < n_out ? n0 + rr : -1;
+    }
+    b_src[i] = n >= 0 ? we + (size_t)n * n_in + chunk * 8 : nullptr;
+  }
+  const int n_k = (n_in + TK - 1) / TK;
+  auto load_stage = [&](int stage, int kt) {
+    const int k0 = kt * TK;
+    const bool kv = k0 + chunk * 8 + 8 <= n_in;
+    const uint32_t a_base = smem_base + stage * (A_BYTES + B_BYTES), b_base = a_base + A_BYTES;
+#pragma unroll
+    for (int i = 0; i < MI; ++i) {
+      const bool ok = kv && a_src[i] != nullptr;
+      cp_async16(a_base + tile_offset((tid >> 3) + i * 32, chunk), ok ? a_src[i] + k0 : a, ok);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const bool ok = kv && b_src[i] != nullptr;
+      cp_async16(b_base + tile_offset((tid >> 3) + i * 32, chunk), ok ? b_src[i] + k0 : w, ok);
+    }
+  };
+  float acc[MI][4][4];
+#pragma unroll
+  for (int i = 0; i < MI; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) acc[i][j][r] = 0.0f;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < n_k) load_stage(s, s);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < n_k; ++kt) {
+    cp_async_wait<STAGES - 2>();
+    __syncthreads();
+    if (kt + STAGES - 1 < n_k) load_stage((kt + STAGES - 1) % STAGES, kt + STAGES - 1);
+    cp_async_commit();
+    const uint32_t a_base = smem_base + (kt % STAGES) * (A_BYTES + B_BYTES), b_base = a_base + A_BYTES;
+#pragma unroll
+    for (int ks = 0; ks < TK / 16; ++ks) {
+      uint32_t af[MI][4], bfr[4][2];
+#pragma unroll
+      for (int i = 0; i < MI; ++i) {
+        const int row = warp_m * (MI * 16) + i * 16 + (lane & 15), ch = ks * 2 + (lane >> 4);
+        ldmatrix_x4(a_base + tile_offset(row, ch), af[i][0], af[i][1], af[i][2], af[i][3]);
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int row = warp_n * 32 + j * 16 + (lane & 7) + ((lane >> 4) << 3);
+        const int ch = ks * 2 + ((lane >> 3) & 1);
+        ldmatrix_x4(b_base + tile_offset(row, ch), bfr[2 * j][0], bfr[2 * j][1], bfr[2 * j + 1][0], bfr[2 * j + 1][1]);
+      }
+#pragma unroll
+      for (int i = 0; i < MI; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], af[i], bfr[j][0], bfr[j][1]);
+    }
+  }
+  cp_async_wait<0>();
+  // a thread holds pairs g and g + 8 and columns 2t, 2t + 1 of every 16 x 8 tile
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int i = 0; i < MI; ++i) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int m = warp_m * (MI * 16) + i * 16 + g + half * 8;
+      if (m >= cnt) continue;
+      if (GATED) {
+        bf16* out = (bf16*)out_ + (size_t)(first + m) * n_out;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int n = n0 + warp_n * 16 + j * 8 + 2 * t + c;
+            if (n < n_out)
+              out[n] = __float2bfloat16(sb_glu_clamped(acc[i][j][half * 2 + c], acc[i][j + 2][half * 2 + c], limit, slope));
+          }
+      } else {
+        float* out = (float*)out_ + (size_t)order[first + m] * n_out;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int n = n0 + warp_n * 32 + j * 8 + 2 * t + c;
+            if (n < n_out) out[n] = acc[i][j][half * 2 + c];
+          }
+      }
+    }
+  }
+}
+
+template <int MI, bool GATED>
+int launch_mma(const void* a, const void* w, const int32_t* order, const int32_t* meta, int tiles, int top, int n_out,
+               int n_in, float limit, float slope, void* out, cudaStream_t stream) {
+  static bool opted = false;
+  if (!opted) {
+    cudaError_t e = cudaFuncSetAttribute(moe_gemm_mma_kernel<MI, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         mma_smem(MI));
+    if (e != cudaSuccess) SB_FAIL(SB_ERR_CUDA, "mixture of experts: shared memory opt-in failed: %s", cudaGetErrorString(e));
+    opted = true;
+  }
+  const dim3 grid(tiles, (n_out + (GATED ? TN / 2 : TN) - 1) / (GATED ? TN / 2 : TN));
+  sb_launch<SB_K_OTHER>(moe_gemm_mma_kernel<MI, GATED>, grid, dim3(MMA_THREADS), (size_t)mma_smem(MI), stream,
+                        (const bf16*)a, (const bf16*)w, order, meta, top, n_out, n_in, limit, slope, out);
+  return SB_OK;
+}
+
 __global__ void moe_combine_kernel(float* x, const float* pair_out, const float* weights, int top, int width) {
   sb_pdl_launch();
   sb_pdl_wait();
@@ -170,32 +398,57 @@ extern "C" int sb_moe_route(const float* logits, int n_rows, int n_experts, int 
                             cudaStream_t stream) {
   if (n_rows <= 0 || n_experts <= 0 || top <= 0 || top > n_experts || !logits || !ids || !weights)
     SB_FAIL(SB_ERR_ARG, "sb_moe_route: rows=%d experts=%d top=%d", n_rows, n_experts, top);
-  sb_launch<SB_K_ELEMENTWISE>(moe_route_kernel, dim3((n_rows + 127) / 128), dim3(128), 0, stream, logits, n_rows, n_experts,
-                              top, ids, weights);
+  if (n_experts <= 1024)
+    sb_launch<SB_K_ELEMENTWISE>(moe_route_warp_kernel, dim3((n_rows + 3) / 4), dim3(128), 0, stream, logits, n_rows,
+                                n_experts, top, ids, weights);
+  else
+    sb_launch<SB_K_ELEMENTWISE>(moe_route_kernel, dim3((n_rows + 127) / 128), dim3(128), 0, stream, logits, n_rows,
+                                n_experts, top, ids, weights);
   SB_CHECK_LAUNCH("sb_moe_route");
   return SB_OK;
 }
 
-extern "C" int sb_moe_max_tiles(int n_pairs, int n_experts) { return (n_pairs + BM - 1) / BM + n_experts; }
+// Pairs of a tile for these sizes: 32 on the plain path; on tensor cores 128 when the experts
+// get about a tile of that size each, else 64.  A choice of speed only: results are the same.
+extern "C" int sb_moe_tile_rows(int dtype, int n_pairs, int n_experts, int ff, int width) {
+  if (dtype != SB_BF16 || ff % 8 || width % 8) return BM;
+  return n_pairs >= 96 * (long long)n_experts ? 128 : 64;
+}
 
-extern "C" int sb_moe_group(const int32_t* ids, int n_pairs, int n_experts, int32_t* order, int32_t* meta,
-                            cudaStream_t stream) {
-  if (n_pairs <= 0 || n_experts <= 0 || !ids || !order || !meta)
-    SB_FAIL(SB_ERR_ARG, "sb_moe_group: pairs=%d experts=%d", n_pairs, n_experts);
+extern "C" int sb_moe_max_tiles(int n_pairs, int n_experts, int tile_rows) {
+  return (n_pairs + tile_rows - 1) / tile_rows + n_experts;
+}
+
+extern "C" int sb_moe_group(const int32_t* ids, int n_pairs, int n_experts, int tile_rows, int32_t* order,
+                            int32_t* meta, cudaStream_t stream) {
+  if (n_pairs <= 0 || n_experts <= 0 || !ids || !order || !meta || (tile_rows != BM && tile_rows != 64 && tile_rows != 128))
+    SB_FAIL(SB_ERR_ARG, "sb_moe_group: pairs=%d experts=%d tile_rows=%d", n_pairs, n_experts, tile_rows);
   const size_t smem = (size_t)3 * n_experts * sizeof(int32_t);
   if (smem > 48 * 1024) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_moe_group: %d experts", n_experts);
-  sb_launch<SB_K_ELEMENTWISE>(moe_group_kernel, dim3(1), dim3(1024), smem, stream, ids, n_pairs, n_experts, order, meta);
+  sb_launch<SB_K_ELEMENTWISE>(moe_group_kernel, dim3(1), dim3(1024), smem, stream, ids, n_pairs, n_experts, tile_rows,
+                              order, meta);
   SB_CHECK_LAUNCH("sb_moe_group");
   return SB_OK;
 }
 
 extern "C" int sb_moe_up(const void* a, int a_dtype, const void* w, int w_dtype, const int32_t* order,
-                         const int32_t* meta, int n_pairs, int n_experts, int top, int ff, int width, float limit,
-                         float slope, void* act, cudaStream_t stream) {
+                         const int32_t* meta, int n_pairs, int n_experts, int tile_rows, int top, int ff, int width,
+                         float limit, float slope, void* act, cudaStream_t stream) {
   if (n_pairs <= 0 || n_experts <= 0 || top <= 0 || ff <= 0 || width <= 0 || !a || !w || !order || !meta || !act)
     SB_FAIL(SB_ERR_ARG, "sb_moe_up: pairs=%d experts=%d top=%d ff=%d width=%d", n_pairs, n_experts, top, ff, width);
   if (!sb_valid_dtype(a_dtype) || a_dtype != w_dtype) SB_FAIL(SB_ERR_ARG, "sb_moe_up: dtype codes %d %d", a_dtype, w_dtype);
-  const dim3 grid(sb_moe_max_tiles(n_pairs, n_experts), (ff + BN - 1) / BN);
+  if (tile_rows != sb_moe_tile_rows(a_dtype, n_pairs, n_experts, ff, width))
+    SB_FAIL(SB_ERR_ARG, "sb_moe_up: tiles of %d pairs are not what sb_moe_tile_rows gives", tile_rows);
+  const int tiles = sb_moe_max_tiles(n_pairs, n_experts, tile_rows);
+  if (tile_rows != BM) {
+    if (((uintptr_t)a | (uintptr_t)w) & 15) SB_FAIL(SB_ERR_ARG, "sb_moe_up: operands must be 16-byte aligned");
+    const int rc = tile_rows == 128 ? launch_mma<4, true>(a, w, order, meta, tiles, top, ff, width, limit, slope, act, stream)
+                                    : launch_mma<2, true>(a, w, order, meta, tiles, top, ff, width, limit, slope, act, stream);
+    if (rc) return rc;
+    SB_CHECK_LAUNCH("sb_moe_up");
+    return SB_OK;
+  }
+  const dim3 grid(tiles, (ff + BN - 1) / BN);
   SB_DISPATCH_DTYPE(a_dtype, T, {
     sb_launch<SB_K_OTHER>(moe_gemm_kernel<T, T, true>, grid, dim3(GEMM_THREADS), 0, stream, (const T*)a, (const T*)w, order,
                           meta, top, ff, width, limit, slope, act);
@@ -205,12 +458,24 @@ extern "C" int sb_moe_up(const void* a, int a_dtype, const void* w, int w_dtype,
 }
 
 extern "C" int sb_moe_down(const void* act, int a_dtype, const void* w, int w_dtype, const int32_t* order,
-                           const int32_t* meta, int n_pairs, int n_experts, int top, int width, int ff,
+                           const int32_t* meta, int n_pairs, int n_experts, int tile_rows, int top, int width, int ff,
                            float* pair_out, cudaStream_t stream) {
   if (n_pairs <= 0 || n_experts <= 0 || top <= 0 || ff <= 0 || width <= 0 || !act || !w || !order || !meta || !pair_out)
     SB_FAIL(SB_ERR_ARG, "sb_moe_down: pairs=%d experts=%d top=%d ff=%d width=%d", n_pairs, n_experts, top, ff, width);
   if (!sb_valid_dtype(a_dtype) || a_dtype != w_dtype) SB_FAIL(SB_ERR_ARG, "sb_moe_down: dtype codes %d %d", a_dtype, w_dtype);
-  const dim3 grid(sb_moe_max_tiles(n_pairs, n_experts), (width + BN - 1) / BN);
+  if (tile_rows != sb_moe_tile_rows(a_dtype, n_pairs, n_experts, ff, width))
+    SB_FAIL(SB_ERR_ARG, "sb_moe_down: tiles of %d pairs are not what sb_moe_tile_rows gives", tile_rows);
+  const int tiles = sb_moe_max_tiles(n_pairs, n_experts, tile_rows);
+  if (tile_rows != BM) {
+    if (((uintptr_t)act | (uintptr_t)w) & 15) SB_FAIL(SB_ERR_ARG, "sb_moe_down: operands must be 16-byte aligned");
+    const int rc = tile_rows == 128
+                       ? launch_mma<4, false>(act, w, order, meta, tiles, top, width, ff, 0.0f, 0.0f, pair_out, stream)
+                       : launch_mma<2, false>(act, w, order, meta, tiles, top, width, ff, 0.0f, 0.0f, pair_out, stream);
+    if (rc) return rc;
+    SB_CHECK_LAUNCH("sb_moe_down");
+    return SB_OK;
+  }
+  const dim3 grid(tiles, (width + BN - 1) / BN);
   SB_DISPATCH_DTYPE(a_dtype, T, {
     sb_launch<SB_K_OTHER>(moe_gemm_kernel<T, T, false>, grid, dim3(GEMM_THREADS), 0, stream, (const T*)act, (const T*)w, order,
                           meta, top, width, ff, 0.0f, 0.0f, (void*)pair_out);

@@ -310,7 +310,8 @@ int sb_ssd_out(const float* o, const float* xbc, int n_rows, int ld, int x_off, 
 
 /* ---- attention with logistic weights (see attn_sigmoid.cu) ---- */
 int sb_attention_sigmoid(const void* q, void* out, int act_dtype, int n_rows, const int32_t* row_seq,
-                         const int32_t* row_pos, const int32_t* page_off, const int32_t* page_ids,
+                         const int32_t* row_pos, int n_seqs, int max_new, const int32_t* seq_row0,
+                         const int32_t* seq_pos0, const int32_t* page_off, const int32_t* page_ids,
                          int page_size, const void* cache, int cache_dtype, int n_q_heads,
                          int n_kv_heads, int hd, int window, int keep_first, float scale, float softcap,
                          const float* head_bias, sb_stream_t stream);
@@ -321,14 +322,16 @@ int sb_attention_sigmoid(const void* q, void* out, int act_dtype, int n_rows, co
  * (in grouped order); pair_out [pairs, width] float32 (in pair order). */
 int sb_moe_route(const float* logits, int n_rows, int n_experts, int top, int32_t* ids, float* weights,
                  sb_stream_t stream);
-int sb_moe_max_tiles(int n_pairs, int n_experts);
-int sb_moe_group(const int32_t* ids, int n_pairs, int n_experts, int32_t* order, int32_t* meta,
+/* Pairs of a tile of one expert (32, 64 or 128) that group, up and down of one step share. */
+int sb_moe_tile_rows(int dtype, int n_pairs, int n_experts, int ff, int width);
+int sb_moe_max_tiles(int n_pairs, int n_experts, int tile_rows);
+int sb_moe_group(const int32_t* ids, int n_pairs, int n_experts, int tile_rows, int32_t* order, int32_t* meta,
                  sb_stream_t stream);
 int sb_moe_up(const void* a, int a_dtype, const void* w, int w_dtype, const int32_t* order,
-              const int32_t* meta, int n_pairs, int n_experts, int top, int ff, int width, float limit,
-              float slope, void* act, sb_stream_t stream);
+              const int32_t* meta, int n_pairs, int n_experts, int tile_rows, int top, int ff, int width,
+              float limit, float slope, void* act, sb_stream_t stream);
 int sb_moe_down(const void* act, int a_dtype, const void* w, int w_dtype, const int32_t* order,
-                const int32_t* meta, int n_pairs, int n_experts, int top, int width, int ff,
+                const int32_t* meta, int n_pairs, int n_experts, int tile_rows, int top, int width, int ff,
                 float* pair_out, sb_stream_t stream);
 int sb_moe_combine(float* x, const float* pair_out, const float* weights, int n_rows, int top, int width,
                    sb_stream_t stream);

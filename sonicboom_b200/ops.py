@@ -1009,13 +1009,15 @@ def attention_sigmoid(q: torch.Tensor, out: torch.Tensor, plan, group_index: int
                       scale: float, softcap: float, head_bias: torch.Tensor | None) -> torch.Tensor:
     """Causal grouped-query attention whose weights are sigmoid(cap(q . k * scale) + head_bias[h]),
     not normalised over the keys, over one cache entry's pages.  Key j is visible to the query at
-    position i when j <= i and (i - j < window or j < keep_first); window 0: every earlier key."""
+    position i when j <= i and (i - j < window or j < keep_first); window 0: every earlier key.
+    bfloat16 at head sizes 64 and 128 runs on tensor cores, everything else the plain kernel."""
     n = q.shape[0]
     g = plan.groups[group_index]
     assert q.dtype == out.dtype and tuple(q.shape) == (n, n_q_heads, head_dim) and out.numel() == q.numel()
     assert head_bias is None or (head_bias.dtype == torch.float32 and head_bias.numel() == n_q_heads)
     _check(lib().sb_attention_sigmoid(
         _ptr(q), _ptr(out), _code(q.dtype), n, _i32(plan.row_seq, "row_seq"), _i32(plan.row_pos, "row_pos"),
+        plan.n_seqs, plan.max_new, _i32(plan.seq_row0, "seq_row0"), _i32(plan.seq_pos0, "seq_pos0"),
         _i32(g.page_off, "page_off"), _i32(g.page_ids, "page_ids"), g.page_size, _ptr(cache), _code(cache.dtype),
         n_q_heads, n_kv_heads, head_dim, window, keep_first, ctypes.c_float(scale), ctypes.c_float(softcap),
         _ptr(head_bias), _stream()), "attention_sigmoid")
@@ -1045,14 +1047,15 @@ def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_up:
     pairs = n * top
     l = lib()
     order = torch.empty(pairs, dtype=torch.int32, device=h.device)
-    meta = torch.empty(1 + 3 * int(l.sb_moe_max_tiles(pairs, n_experts)), dtype=torch.int32, device=h.device)
+    tile = int(l.sb_moe_tile_rows(_code(h.dtype), pairs, n_experts, ff, width))
+    meta = torch.empty(1 + 3 * int(l.sb_moe_max_tiles(pairs, n_experts, tile)), dtype=torch.int32, device=h.device)
     act = torch.empty((pairs, ff), dtype=h.dtype, device=h.device)
     pair_out = torch.empty((pairs, width), dtype=torch.float32, device=h.device)
-    _check(l.sb_moe_group(_ptr(ids), pairs, n_experts, _ptr(order), _ptr(meta), _stream()), "moe_group")
+    _check(l.sb_moe_group(_ptr(ids), pairs, n_experts, tile, _ptr(order), _ptr(meta), _stream()), "moe_group")
     _check(l.sb_moe_up(_ptr(h), _code(h.dtype), _ptr(w_up), _code(w_up.dtype), _ptr(order), _ptr(meta), pairs,
-                       n_experts, top, ff, width, ctypes.c_float(limit), ctypes.c_float(slope), _ptr(act),
+                       n_experts, tile, top, ff, width, ctypes.c_float(limit), ctypes.c_float(slope), _ptr(act),
                        _stream()), "moe_up")
     _check(l.sb_moe_down(_ptr(act), _code(act.dtype), _ptr(w_down), _code(w_down.dtype), _ptr(order), _ptr(meta),
-                         pairs, n_experts, top, width, ff, _ptr(pair_out), _stream()), "moe_down")
+                         pairs, n_experts, tile, top, width, ff, _ptr(pair_out), _stream()), "moe_down")
     _check(l.sb_moe_combine(_ptr(x), _ptr(pair_out), _ptr(weights), n, top, width, _stream()), "moe_combine")
     return x

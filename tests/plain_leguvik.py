@@ -107,6 +107,7 @@ def general_delta(h, get, m, eps):
 
 
 def visible(i, j, size, keep_first):
+    """Whether the query at position i sees the key at position j."""
     return j <= i and (i - j < size or j < keep_first)
 
 
@@ -117,17 +118,16 @@ def sigmoid_attention(h, get, m, keys=None, values=None):
     q = (h @ get("q").T).view(T, H, K)
     if keys is None:
         keys, values = (h @ get("k").T).view(T, G, K), (h @ get("v").T).view(T, G, V)
-    cap, pb = m["softcap"], get("pb")
+    cap, pb = m.get("softcap", 0.0), get("pb")
     out = torch.zeros(T, H, V, dtype=F)
     for i in range(T):
+        seen = [j for j in range(T) if visible(i, j, m["mask"]["size"], m["mask"].get("keep_first", 0))]
         for hh in range(H):
             g = hh // (H // G)
-            for j in range(i + 1):
-                if not visible(i, j, m["mask"]["size"], m["mask"]["keep_first"]):
-                    continue
-                s = (q[i, hh] @ keys[j, g]) * m["scale"]
+            s = (keys[seen, g] @ q[i, hh]) * m["scale"]
+            if cap:
                 s = cap * torch.tanh(s / cap)
-                out[i, hh] += torch.sigmoid(s + pb[hh]) * values[j, g]
+            out[i, hh] = torch.sigmoid(s + pb[hh]) @ values[seen, g]
     return out.reshape(T, H * V) @ get("o").T, keys, values
 
 
@@ -159,14 +159,19 @@ def forward(cfg, tensors, tokens, streams=None):
     def getter(prefix):
         return lambda name: tensors[prefix + name].to(F)
     eps = cfg["norm"]["eps"]
-    bg = cfg["embedding"]["bigram"]
-    x = embed(tokens, tensors["embed"], tensors["bigram"], bg["buckets"], bg["mul_prev"], bg["mul_cur"])
+    bg = (cfg.get("embedding") or {}).get("bigram")
+    if bg:
+        x = embed(tokens, tensors["embed"], tensors["bigram"], bg["buckets"], bg["mul_prev"], bg["mul_cur"])
+    else:
+        x = tensors["embed"][torch.tensor(list(tokens), dtype=torch.long)].to(F)
+    canon = "canon" in cfg
     kept = {}
     for i, L in enumerate(cfg["layers"]):
         p = f"l{i}."
         m = L["mixer"]
         h = layer_norm(x, tensors[p + "norm1"].to(F), eps)
-        h = h + causal_conv(h, tensors[p + "canon1"].to(F))
+        if canon:
+            h = h + causal_conv(h, tensors[p + "canon1"].to(F))
         get = getter(p + "mix.")
         if L["type"] == "mamba2":
             x = x + mamba2(h, get, m, eps)
@@ -181,11 +186,19 @@ def forward(cfg, tensors, tokens, streams=None):
             raise ValueError(L["type"])
         if L.get("mlp") is not None:
             h = layer_norm(x, tensors[p + "norm2"].to(F), eps)
-            h = h + causal_conv(h, tensors[p + "canon2"].to(F))
+            if canon:
+                h = h + causal_conv(h, tensors[p + "canon2"].to(F))
             x = x + moe(h, getter(p + "mlp."), L["mlp"])
         if streams is not None:
             streams.append(x.clone())
     hn = layer_norm(x, tensors["final.norm"].to(F), eps)
     logits = hn @ tensors["head"].to(F).T
-    cap = cfg["logit_softcap"]
-    return cap * torch.tanh(logits / cap)
+    cap = cfg.get("logit_softcap", 0.0)
+    return cap * torch.tanh(logits / cap) if cap else logits
+
+
+def greedy_generate(cfg, tensors, prompt, n_new):
+    seq = list(prompt)
+    for _ in range(n_new):
+        seq.append(int(torch.argmax(forward(cfg, tensors, seq)[-1])))
+    return seq[len(prompt):]

@@ -878,6 +878,9 @@ def leguvik_kernels(bench, z, rows, context):
     rec(f"like: attention, softmax ({kind}; window {win})",
         timed(lambda: ops.attention(q, o, plan, cache.group_of_entry[1], store1, H, G, d, win, d ** -0.5)),
         att_bytes, att_flops)
+    rec(f"like: attention, softmax, the mma.sync kernels ({kind}; window {win})",
+        timed(lambda: ops.attention(q, o, plan, cache.group_of_entry[1], store1, H, G, d, win, d ** -0.5, kernel="mma")),
+        att_bytes, att_flops)
     # delta rule
     rank = 32
     dproj = torch.randn(rows, 5 * hk + rank, device=dev) * 0.1

@@ -15,7 +15,8 @@
 // cp.async pipeline: the pages of the kept first keys that lie before the window, then the
 // window's.  A weight is rounded to bfloat16 only as the operand of the second product.  Tiles
 // lie at absolute positions and a key that a row does not see adds an exact zero, so a row's sum
-// does not depend on the rows around it.
+// does not depend on the rows around it.  With at most 16 rows for a sequence and key/value head
+// (decoding) a block's tiles are two pages wide and its 8 warps share every tile's keys.
 #include <math.h>
 
 #include "common.cuh"
@@ -296,6 +297,159 @@ __global__ void __launch_bounds__(TC_THREADS) attn_sigmoid_mma_kernel(const Sigm
   }
 }
 
+// At most 16 rows for a sequence and key/value head (decoding): one block, whose tiles are two
+// pages (128 keys) wide; each of the 8 warps takes 16 keys of every tile for all rows, and the
+// warps' sums are added in warp order at the end.
+constexpr int DEC_ROWS = 16, DEC_KEYS = 2 * KT;
+template <int HD>
+constexpr int dec_smem() { return (DEC_ROWS + 4 * DEC_KEYS) * (HD + 8) * 2; }
+
+template <int HD>
+__global__ void __launch_bounds__(TC_THREADS) attn_sigmoid_mma_decode_kernel(const SigmoidParams p) {
+  constexpr int LDS = HD + 8;
+  static_assert(TC_THREADS / 32 * 16 == DEC_KEYS, "a warp for every 16 keys of a tile");
+  static_assert(TC_THREADS / 32 * DEC_ROWS * HD * 4 <= 4 * DEC_KEYS * LDS * 2, "the warps' sums fit the tiles' space");
+  extern __shared__ __align__(128) unsigned char smem[];
+  const uint32_t qs = (uint32_t)__cvta_generic_to_shared(smem);
+  const uint32_t kv0 = qs + DEC_ROWS * LDS * 2;               // K0, V0, K1, V1 of 128 keys each
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.z, kvh = blockIdx.x;
+  const int G = p.n_q_heads / p.n_kv_heads;
+  const int row0 = p.seq_row0[b], n_new = p.seq_row0[b + 1] - row0, pos0 = p.seq_pos0[b];
+  const int R = n_new * G;
+  if (R <= 0) return;
+  if (pos0 < 0 || (pos0 + n_new - 1) / KT >= p.page_off[b + 1] - p.page_off[b]) {
+    for (int idx = tid; idx < R * HD; idx += TC_THREADS)
+      p.out[((size_t)(row0 + idx / HD / G) * p.n_q_heads + kvh * G + idx / HD % G) * HD + idx % HD] = __float2bfloat16(0.0f);
+    return;
+  }
+  const int32_t* pages = p.page_ids + p.page_off[b];
+  const int p_hi = pos0 + n_new - 1;
+  const int tile_lo = (p.window > 0 ? max(0, pos0 - p.window + 1) : 0) / KT, tile_hi = p_hi / KT;
+  const int n_kept = p.window > 0 && p.keep_first > 0 ? min((p.keep_first - 1) / KT + 1, tile_lo) : 0;
+  const int n_pages = n_kept + tile_hi - tile_lo + 1, n_tiles = (n_pages + 1) / 2;
+  auto page_at = [&](int i) { return i < n_kept ? i : tile_lo + i - n_kept; };
+  auto load_tile = [&](int stage, int it) {
+    const uint32_t ks = kv0 + stage * 2 * DEC_KEYS * LDS * 2, vs = ks + DEC_KEYS * LDS * 2;
+    for (int idx = tid; idx < DEC_KEYS * (HD / 8); idx += TC_THREADS) {
+      const int row = idx / (HD / 8), ch = idx % (HD / 8);
+      const int pi = 2 * it + row / KT;
+      const bool ok = pi < n_pages;                            // an odd last page: zeros beside it
+      const bf16* kbase = p.cache + (((size_t)(ok ? pages[page_at(pi)] : 0) * 2) * p.n_kv_heads + kvh) * (size_t)(KT * HD);
+      const bf16* vbase = kbase + (size_t)p.n_kv_heads * (KT * HD);
+      const uint32_t off = (uint32_t)(row * LDS + ch * 8) * 2;
+      cp_async16(ks + off, kbase + (row % KT) * HD + ch * 8, ok);
+      cp_async16(vs + off, vbase + (row % KT) * HD + ch * 8, ok);
+    }
+  };
+  for (int idx = tid; idx < DEC_ROWS * (HD / 8); idx += TC_THREADS) {
+    const int row = idx / (HD / 8), ch = idx % (HD / 8);
+    const bool valid = row < R;
+    const int t = valid ? row / G : 0, g = valid ? row % G : 0;
+    cp_async16(qs + (uint32_t)(row * LDS + ch * 8) * 2,
+               p.q + ((size_t)(row0 + t) * p.n_q_heads + kvh * G + g) * HD + ch * 8, valid);
+  }
+  load_tile(0, 0);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+  uint32_t qf[HD / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < HD / 16; ++kk) {
+    const int row = lane & 15, col = kk * 16 + (lane >> 4) * 8;
+    ldmatrix_x4(qs + (uint32_t)(row * LDS + col) * 2, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+  }
+  const int ra = lane >> 2, rb = ra + 8;
+  const int pos_a = ra < R ? pos0 + ra / G : -1, pos_b = rb < R ? pos0 + rb / G : -1;
+  const float pb_a = p.head_bias && ra < R ? p.head_bias[kvh * G + ra % G] : 0.0f;
+  const float pb_b = p.head_bias && rb < R ? p.head_bias[kvh * G + rb % G] : 0.0f;
+  const float two_inv_cap = p.softcap > 0.0f ? 2.0f / p.softcap : 0.0f;
+  float o[HD / 8][4];
+#pragma unroll
+  for (int j = 0; j < HD / 8; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[j][i] = 0.0f;
+  const int krow0 = warp * 16;                                 // this warp's keys of every tile
+  for (int it = 0; it < n_tiles; ++it) {
+    const int stage = it & 1;
+    const uint32_t ks = kv0 + stage * 2 * DEC_KEYS * LDS * 2, vs = ks + DEC_KEYS * LDS * 2;
+    if (it + 1 < n_tiles) {
+      load_tile(stage ^ 1, it + 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int pi = 2 * it + krow0 / KT;
+    if (pi < n_pages) {
+      const int key0 = page_at(pi) * KT + krow0 % KT;
+      float s[2][4];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[j][i] = 0.0f;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; ++kk) {
+        const int row = krow0 + (lane & 7) + ((lane >> 4) << 3);
+        const int col = kk * 16 + ((lane >> 3) & 1) * 8;
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(ks + (uint32_t)(row * LDS + col) * 2, b0, b1, b2, b3);
+        mma_bf16(s[0], qf[kk], b0, b1);
+        mma_bf16(s[1], qf[kk], b2, b3);
+      }
+      const int t = lane & 3;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int key = key0 + j * 8 + 2 * t + (i & 1);
+          const int pos = (i < 2) ? pos_a : pos_b;
+          const bool seen = key <= pos && (p.window == 0 || pos - key < p.window || key < p.keep_first);
+          float v = s[j][i] * p.scale;
+          if (p.softcap > 0.0f) v = p.softcap * (1.0f - __fdividef(2.0f, __expf(fminf(v * two_inv_cap, 80.0f)) + 1.0f));
+          v += (i < 2) ? pb_a : pb_b;
+          s[j][i] = seen ? __fdividef(1.0f, 1.0f + __expf(fminf(-v, 80.0f))) : 0.0f;
+        }
+      }
+      uint32_t a[4];
+      a[0] = pack_bf16(s[0][0], s[0][1]);
+      a[1] = pack_bf16(s[0][2], s[0][3]);
+      a[2] = pack_bf16(s[1][0], s[1][1]);
+      a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+      for (int dj = 0; dj < HD / 16; ++dj) {
+        const int row = krow0 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int col = dj * 16 + (lane >> 4) * 8;
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4_trans(vs + (uint32_t)(row * LDS + col) * 2, b0, b1, b2, b3);
+        mma_bf16(o[2 * dj], a, b0, b1);
+        mma_bf16(o[2 * dj + 1], a, b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+  // the warps' sums, added in warp order
+  float* part = reinterpret_cast<float*>(smem + DEC_ROWS * LDS * 2);
+  const int t4 = lane & 3;
+#pragma unroll
+  for (int j = 0; j < HD / 8; ++j) {
+    float* dst = part + ((size_t)warp * DEC_ROWS) * HD + j * 8 + 2 * t4;
+    dst[ra * HD] = o[j][0], dst[ra * HD + 1] = o[j][1];
+    dst[rb * HD] = o[j][2], dst[rb * HD + 1] = o[j][3];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < R * HD; idx += TC_THREADS) {
+    float sum = 0.0f;
+#pragma unroll
+    for (int w = 0; w < TC_THREADS / 32; ++w) sum += part[(size_t)w * DEC_ROWS * HD + idx];
+    const int r = idx / HD;
+    p.out[((size_t)(row0 + r / G) * p.n_q_heads + kvh * G + r % G) * HD + idx % HD] = __float2bfloat16(sum);
+  }
+}
+
 template <int HD>
 int launch_sigmoid_mma(const SigmoidParams& p, int n_seqs, int max_new, cudaStream_t stream) {
   static bool opted = false;
@@ -306,6 +460,18 @@ int launch_sigmoid_mma(const SigmoidParams& p, int n_seqs, int max_new, cudaStre
     opted = true;
   }
   const int G = p.n_q_heads / p.n_kv_heads;
+  if (max_new * G <= DEC_ROWS) {
+    static bool dec_opted = false;
+    if (!dec_opted) {
+      cudaError_t e = cudaFuncSetAttribute(attn_sigmoid_mma_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           dec_smem<HD>());
+      if (e != cudaSuccess) SB_FAIL(SB_ERR_CUDA, "sb_attention_sigmoid: shared memory opt-in failed: %s", cudaGetErrorString(e));
+      dec_opted = true;
+    }
+    sb_launch(attn_sigmoid_mma_decode_kernel<HD>, dim3(p.n_kv_heads, 1, n_seqs), dim3(TC_THREADS), (size_t)dec_smem<HD>(),
+              stream, p);
+    return SB_OK;
+  }
   const int row_blocks = (max_new * G + TC_BM - 1) / TC_BM;
   const dim3 grid(row_blocks * p.n_kv_heads, 1, n_seqs);
   sb_launch(attn_sigmoid_mma_kernel<HD>, grid, dim3(TC_THREADS), (size_t)tc_smem<HD>(), stream, p);

@@ -12,18 +12,19 @@
 //                  a = sigmoid(a_raw + a_bias) times the unit key, and the unit key, into
 //                  aux [rows, 3, heads * dim] (w | a * u | u)
 //   sb_delta_scan: the recurrence token by token in float32, for prompts, portions and single
-//                  tokens alike.  A column is shared by eight lanes that keep their channels of it
-//                  in registers for the whole step; a block has sixteen such groups; tokens are
+//                  tokens alike.  A column is shared by sixteen lanes that keep their channels of it
+//                  in registers for the whole step; a block has eight such groups; tokens are
 //                  staged sixteen at a time in shared memory, one or two groups ahead of the one
-//                  in work (cp.async).  State: float32 [slot, heads, dim(value), dim(key)].
+//                  in work (cp.async).  Only u . s, which the update needs, is summed over the
+//                  lanes token by token; the lanes' parts of the outputs wait for the group's end.  State: float32 [slot, heads, dim(value), dim(key)].
 #include <math.h>
 
 #include "common.cuh"
 
 namespace {
 
-constexpr int LPC = 8;               // lanes that share a column
-constexpr int COLS = 16;             // columns of a block
+constexpr int LPC = 16;              // lanes that share a column
+constexpr int COLS = 8;              // columns of a block
 constexpr int THREADS = LPC * COLS;  // 128
 constexpr int TB = 16;               // tokens staged together
 
@@ -111,7 +112,7 @@ __device__ __forceinline__ void delta_cp_async(float* dst, const float* src, boo
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
 }
 
-// NPL channels per lane: lane `sub` of a column keeps channels sub + 8 i.  Groups of TB tokens
+// NPL channels per lane: lane `sub` of a column keeps channels sub + 16 i.  Groups of TB tokens
 // are staged STAGES - 1 groups ahead with cp.async (in pieces of VEC floats: 4 where every row,
 // offset and head size is a multiple of 4 floats, else 1), so the loads of later tokens are in
 // flight while the recurrence, a chain from token to token, runs.
@@ -127,8 +128,10 @@ delta_scan_kernel(const float* proj, int ld, int r_off, int k_off, int v_off, co
   const int tid = threadIdx.x, sub = tid % LPC, cl = tid / LPC;
   const int col0 = blockIdx.x * COLS, col = col0 + cl;
   const int hk = n_heads * dim;
-  for (int i = tid; i < STAGES * TB * ROW; i += THREADS) smem[i] = 0.0f;     // padding stays zero for good
-  __syncthreads();
+  if (PAD > dim) {                                 // channels past the head's size stay zero for good
+    for (int i = tid; i < STAGES * TB * ROW; i += THREADS) smem[i] = 0.0f;
+    __syncthreads();
+  }
   sb_pdl_wait();
   const int row0 = seq_row0[b], n = seq_row0[b + 1] - row0;
   const int slot = seq_slot[b];
@@ -136,20 +139,25 @@ delta_scan_kernel(const float* proj, int ld, int r_off, int k_off, int v_off, co
   auto stage = [&](int buf, int t0) {
     const int cnt = min(TB, n - t0);
     float* base = smem + buf * TB * ROW;
-    for (int e = tid; e < cnt * per_tok; e += THREADS) {
-      const int tt = e / per_tok, rest = e - tt * per_tok;
-      const size_t rw = (size_t)(row0 + t0 + tt);
-      if (rest < 5 * dimv) {
-        const int arr = rest / dimv, c = (rest - arr * dimv) * VEC;
-        const float* src = arr == 0   ? proj + rw * ld + r_off + h * dim + c
-                           : arr == 1 ? proj + rw * ld + k_off + h * dim + c
-                                      : aux + rw * 3 * hk + (size_t)(arr - 2) * hk + h * dim + c;
-        delta_cp_async<VEC>(base + tt * ROW + arr * PAD + c, src, true);
+    // a thread keeps to its pieces of a token and walks over the group's tokens
+    for (int q = tid; q < per_tok; q += THREADS) {
+      const float* src;
+      size_t stride;
+      float* dst;
+      bool ok = true;
+      if (q < 5 * dimv) {
+        const int arr = q / dimv, c = (q - arr * dimv) * VEC;
+        const size_t rw = (size_t)(row0 + t0);
+        if (arr < 2) src = proj + rw * ld + (arr == 0 ? r_off : k_off) + h * dim + c, stride = ld;
+        else src = aux + rw * 3 * hk + (size_t)(arr - 2) * hk + h * dim + c, stride = (size_t)3 * hk;
+        dst = base + arr * PAD + c;
       } else {
-        const int c = (rest - 5 * dimv) * VEC;
-        const bool ok = col0 + c < dim;
-        delta_cp_async<VEC>(base + tt * ROW + 5 * PAD + c, ok ? proj + rw * ld + v_off + h * dim + col0 + c : proj, ok);
+        const int c = (q - 5 * dimv) * VEC;
+        ok = col0 + c < dim;
+        src = ok ? proj + (size_t)(row0 + t0) * ld + v_off + h * dim + col0 + c : proj, stride = ok ? ld : 0;
+        dst = base + 5 * PAD + c;
       }
+      for (int tt = 0; tt < cnt; ++tt) delta_cp_async<VEC>(dst + tt * ROW, src + tt * stride, ok);
     }
   };
   const int n_groups = (n + TB - 1) / TB;
@@ -172,30 +180,63 @@ delta_scan_kernel(const float* proj, int ld, int r_off, int k_off, int v_off, co
     if (gi + STAGES - 1 < n_groups) stage((gi + STAGES - 1) % STAGES, (gi + STAGES - 1) * TB);
     asm volatile("cp.async.commit_group;\n");
     const float* grp = smem + (gi % STAGES) * TB * ROW;
-    for (int tt = 0; tt < cnt; ++tt) {
-      const float* tok = grp + tt * ROW;
-      const float v = tok[5 * PAD + cl];
-      float d = 0.0f;
+    float op[TB];                                  // this lane's part of every token's o . r
 #pragma unroll
-      for (int i = 0; i < NPL; ++i) d = fmaf(tok[4 * PAD + sub + LPC * i], S[i], d);       // u . s (old state)
-      d += __shfl_xor_sync(0xffffffffu, d, 4);
-      d += __shfl_xor_sync(0xffffffffu, d, 2);
-      d += __shfl_xor_sync(0xffffffffu, d, 1);
-      float o = 0.0f;
+    for (int tt = 0; tt < TB; ++tt) {
+      op[tt] = 0.0f;
+      if (tt < cnt) {
+        const float* tok = grp + tt * ROW;
+        const float v = tok[5 * PAD + cl];
+        float d0 = 0.0f, d1 = 0.0f;                // u . s (old state), even and odd pieces apart
 #pragma unroll
-      for (int i = 0; i < NPL; ++i) {
-        const int c = sub + LPC * i;
-        float s = tok[2 * PAD + c] * S[i];
-        s = fmaf(-tok[3 * PAD + c], d, s);
-        s = fmaf(tok[PAD + c], v, s);
-        S[i] = s;
-        o = fmaf(s, tok[c], o);
+        for (int i = 0; i < NPL; i += 2) {
+          d0 = fmaf(tok[4 * PAD + sub + LPC * i], S[i], d0);
+          d1 = fmaf(tok[4 * PAD + sub + LPC * (i + 1)], S[i + 1], d1);
+        }
+        float d = d0 + d1;
+        d += __shfl_xor_sync(0xffffffffu, d, 8);
+        d += __shfl_xor_sync(0xffffffffu, d, 4);
+        d += __shfl_xor_sync(0xffffffffu, d, 2);
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        float o0 = 0.0f, o1 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NPL; i += 2) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int c = sub + LPC * (i + e);
+            float s = tok[2 * PAD + c] * S[i + e];
+            s = fmaf(-tok[3 * PAD + c], d, s);
+            s = fmaf(tok[PAD + c], v, s);
+            S[i + e] = s;
+            if (e == 0) o0 = fmaf(s, tok[c], o0);
+            else o1 = fmaf(s, tok[c], o1);
+          }
+        }
+        op[tt] = o0 + o1;
       }
-      o += __shfl_xor_sync(0xffffffffu, o, 4);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      if (sub == 0 && col < dim) out[((size_t)(row0 + t0 + tt) * n_heads + h) * dim + col] = o;
     }
+    // the sixteen lanes of a column add their parts of the group's sixteen sums in four rounds of
+    // exchanges, halving what a lane keeps each time: the same tree of additions for every token,
+    // and lane `sub` ends with the sum of token `sub`
+    float a8[8], a4[4], a2[2];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float mine = (sub & 8) ? op[8 + j] : op[j], other = (sub & 8) ? op[j] : op[8 + j];
+      a8[j] = mine + __shfl_xor_sync(0xffffffffu, other, 8);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float mine = (sub & 4) ? a8[4 + j] : a8[j], other = (sub & 4) ? a8[j] : a8[4 + j];
+      a4[j] = mine + __shfl_xor_sync(0xffffffffu, other, 4);
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const float mine = (sub & 2) ? a4[2 + j] : a4[j], other = (sub & 2) ? a4[j] : a4[2 + j];
+      a2[j] = mine + __shfl_xor_sync(0xffffffffu, other, 2);
+    }
+    const float mine1 = (sub & 1) ? a2[1] : a2[0], other1 = (sub & 1) ? a2[0] : a2[1];
+    const float sum = mine1 + __shfl_xor_sync(0xffffffffu, other1, 1);
+    if (sub < cnt && col < dim) out[((size_t)(row0 + t0 + sub) * n_heads + h) * dim + col] = sum;
   }
   asm volatile("cp.async.wait_group 0;\n");
   if (col < dim) {
@@ -211,7 +252,7 @@ template <int NPL, int VEC>
 cudaError_t launch_delta(dim3 grid, cudaStream_t stream, const float* proj, int ld, int r_off, int k_off, int v_off,
                          const float* aux, const int32_t* seq_row0, const int32_t* seq_slot, int n_heads, int dim,
                          float* state, float* out) {
-  constexpr int STAGES = NPL >= 32 ? 2 : 3;
+  constexpr int STAGES = NPL >= 16 ? 2 : 3;
   constexpr size_t smem = (size_t)STAGES * TB * (5 * NPL * LPC + COLS) * sizeof(float);
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
@@ -253,7 +294,7 @@ extern "C" int sb_delta_scan(const float* proj, int ld, int r_off, int k_off, in
                              float* out, cudaStream_t stream) {
   if (n_seqs <= 0 || n_heads <= 0 || dim <= 0 || !proj || !aux || !state || !out || !seq_row0 || !seq_slot)
     SB_FAIL(SB_ERR_ARG, "sb_delta_scan: seqs=%d heads=%d dim=%d", n_seqs, n_heads, dim);
-  if (dim > 32 * LPC) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_delta_scan: head size %d is above %d", dim, 32 * LPC);
+  if (dim > 16 * LPC) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_delta_scan: head size %d is above %d", dim, 16 * LPC);
   if (n_heads > 65535 || n_seqs > 65535) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_delta_scan: %d heads, %d sequences", n_heads, n_seqs);
   const dim3 grid((dim + COLS - 1) / COLS, n_heads, n_seqs);
   const int npl = (dim + LPC - 1) / LPC;
@@ -264,8 +305,7 @@ extern "C" int sb_delta_scan(const float* proj, int ld, int r_off, int k_off, in
   if (npl <= 2) e = SB_DELTA_PICK(2);
   else if (npl <= 4) e = SB_DELTA_PICK(4);
   else if (npl <= 8) e = SB_DELTA_PICK(8);
-  else if (npl <= 16) e = SB_DELTA_PICK(16);
-  else e = SB_DELTA_PICK(32);
+  else e = SB_DELTA_PICK(16);
 #undef SB_DELTA_PICK
 #undef SB_DELTA_ARGS
   if (e != cudaSuccess) SB_FAIL(SB_ERR_CUDA, "sb_delta_scan: launch failed: %s", cudaGetErrorString(e));

@@ -238,7 +238,7 @@ constexpr int mma_smem(int mi) { return STAGES * (mi * 32 + TN) * TK * 2; }
 // a block finishes 64 outputs.  Else 128 outputs of the down product.  Every output is summed over
 // the inner values in the same order whatever the tile, the pair's place in it, or MI.
 template <int MI, bool GATED>
-__global__ void __launch_bounds__(MMA_THREADS)
+__global__ void __launch_bounds__(MMA_THREADS, 2)
 moe_gemm_mma_kernel(const bf16* a, const bf16* __restrict__ w, const int32_t* order, const int32_t* meta, int top,
                     int n_out, int n_in, float limit, float slope, void* out_) {
   constexpr int TM = MI * 32;

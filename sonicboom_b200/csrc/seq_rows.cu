@@ -124,6 +124,51 @@ __global__ void causal_conv_kernel(const float* x, int ld, int x_off, int channe
   }
 }
 
+// The same sums for a step with several rows a sequence and at most CONV_MAXT taps: a thread walks
+// CONV_RUN consecutive rows of its channel and keeps the last taps - 1 inputs in registers, so a row
+// is read once instead of once per tap.  Every sum has the order of the kernel above.
+constexpr int CONV_MAXT = 8, CONV_RUN = 8;
+template <typename TW, typename TO>
+__global__ void causal_conv_run_kernel(const float* x, int n_rows, int ld, int x_off, int channels, int taps,
+                                       const TW* __restrict__ w, const TW* __restrict__ bias, int act, int add_input,
+                                       const int32_t* row_seq, const int32_t* row_pos, const int32_t* seq_pos0,
+                                       const int32_t* seq_slot, const float* state, TO* out, int ld_out, int out_off) {
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int r_begin = blockIdx.x * CONV_RUN, r_end = min(n_rows, r_begin + CONV_RUN);
+  float wd[CONV_MAXT], hist[CONV_MAXT];     // by distance d: the weight of x_(t - d); hist[d] = x of the row d before
+#pragma unroll
+  for (int d = 0; d < CONV_MAXT; ++d) {
+    wd[d] = d < taps ? sb_to_f32<TW>(w[(size_t)c * taps + (taps - 1 - d)]) : 0.0f;
+    hist[d] = (d >= 1 && d < taps && r_begin - d >= 0) ? x[(size_t)(r_begin - d) * ld + x_off + c] : 0.0f;
+  }
+  const float b = bias ? sb_to_f32<TW>(bias[c]) : 0.0f;
+  for (int r = r_begin; r < r_end; ++r) {
+    const int s = row_seq[r], pos = row_pos[r], pos0 = seq_pos0[s];
+    const float* st = state ? state + (size_t)seq_slot[s] * (taps - 1) * channels + c : nullptr;
+    const float cur = x[(size_t)r * ld + x_off + c];
+    hist[0] = cur;
+    float acc = b;
+#pragma unroll
+    for (int d = CONV_MAXT - 1; d >= 0; --d) {
+      if (d < taps) {
+        const int p = pos - d;
+        float v = 0.0f;
+        if (p >= pos0) v = hist[d];
+        else if (p >= 0) v = st[(size_t)(p - pos0 + taps - 1) * channels];
+        acc = fmaf(wd[d], v, acc);
+      }
+    }
+    if (add_input) acc += cur;
+    if (act) acc = sb_silu(acc);
+    out[(size_t)r * ld_out + out_off + c] = sb_from_f32<TO>(acc);
+#pragma unroll
+    for (int d = CONV_MAXT - 1; d >= 1; --d) hist[d] = hist[d - 1];
+  }
+}
+
 __global__ void conv_state_kernel(const float* x, int ld, int x_off, int channels, int taps,
                                   const int32_t* seq_row0, const int32_t* seq_slot, float* state) {
   sb_pdl_launch();
@@ -203,7 +248,12 @@ extern "C" int sb_causal_conv(const float* x, int n_rows, int ld, int x_off, int
   const bool own = n_rows == n_seqs;        // one row a sequence: the row's threads shift the state themselves
   SB_DISPATCH_DTYPE(w_dtype, TW, {
     SB_DISPATCH_DTYPE(out_dtype, TO, {
-      if (own)
+      if (!own && taps <= CONV_MAXT)
+        sb_launch<SB_K_ELEMENTWISE>(causal_conv_run_kernel<TW, TO>, dim3((n_rows + CONV_RUN - 1) / CONV_RUN, grid.y), dim3(nt),
+                                    0, stream, x, n_rows, ld, x_off, channels, taps, (const TW*)w, (const TW*)bias, act,
+                                    add_input, row_seq, row_pos, seq_pos0, seq_slot, (const float*)state, (TO*)out, ld_out,
+                                    out_off);
+      else if (own)
         sb_launch<SB_K_ELEMENTWISE>(causal_conv_kernel<TW, TO, true>, grid, dim3(nt), 0, stream, x, ld, x_off, channels,
                                     taps, (const TW*)w, (const TW*)bias, act, add_input, row_seq, row_pos, seq_row0,
                                     seq_pos0, seq_slot, state, (TO*)out, ld_out, out_off);

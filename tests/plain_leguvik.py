@@ -137,10 +137,15 @@ def clamped_glu(h, gate, up, down, limit):
     return (g * torch.sigmoid(GLU_SLOPE * g) * (u + 1)) @ down.T
 
 
-def moe(h, get, m):
+def moe(h, get, m, gaps=None):
+    """`gaps` (a list) receives, per token, the gap between the last chosen logit and the largest one
+    that was not chosen (infinite when every expert is chosen)."""
     E, top = m["router"]["experts"], m["router"]["top"]
     T = h.shape[0]
     z = h @ get("router").T + get("router.b")
+    if gaps is not None:
+        ranked = z.sort(dim=1, descending=True).values
+        gaps.append(ranked[:, top - 1] - ranked[:, top] if top < E else torch.full((T,), float("inf"), dtype=F))
     out = torch.zeros(T, get("e0.down").shape[0], dtype=F)
     for t in range(T):
         order = sorted(range(E), key=lambda e: (-float(z[t, e]), e))[:top]
@@ -153,9 +158,9 @@ def moe(h, get, m):
     return out
 
 
-def forward(cfg, tensors, tokens, streams=None):
+def forward(cfg, tensors, tokens, streams=None, gaps=None):
     """float64 logits [T, vocab] of one sequence; `streams` (a list) receives the residual stream
-    after every layer."""
+    after every layer, `gaps` (a list) every experts layer's router gaps per token (see `moe`)."""
     def getter(prefix):
         return lambda name: tensors[prefix + name].to(F)
     eps = cfg["norm"]["eps"]
@@ -188,7 +193,7 @@ def forward(cfg, tensors, tokens, streams=None):
             h = layer_norm(x, tensors[p + "norm2"].to(F), eps)
             if canon:
                 h = h + causal_conv(h, tensors[p + "canon2"].to(F))
-            x = x + moe(h, getter(p + "mlp."), L["mlp"])
+            x = x + moe(h, getter(p + "mlp."), L["mlp"], gaps)
         if streams is not None:
             streams.append(x.clone())
     hn = layer_norm(x, tensors["final.norm"].to(F), eps)

@@ -33,8 +33,35 @@ def rel_err(got, ref):
     return float(d.pow(2).mean(-1).sqrt().max() / ref.pow(2).mean().sqrt().clamp_min(1e-30))
 
 
+CLOSE = {}                # id of a reference -> rows that a close call of a router may have moved
+CLOSE_GAP, CLOSE_REACH = 0.02, 4
+
+
+def reference(cfg, tensors, toks):
+    """The plain implementation's logits.  It also notes where a router's choice was close (the
+    gap to the best expert not chosen below CLOSE_GAP, a few times what bfloat16 rounding moves
+    a logit by): there the bfloat16 model may choose another expert, which is no fault; the input
+    convolutions spread the difference over the next rows (CLOSE_REACH rows are excused), and what
+    the recurrent states carry on from there stays within the tolerance."""
+    gaps = []
+    ref = pl.forward(cfg, tensors, toks, gaps=gaps)
+    close = torch.zeros(len(toks), dtype=torch.bool)
+    for t in (torch.nonzero(torch.stack(gaps).min(0).values < CLOSE_GAP).flatten().tolist() if gaps else []):
+        close[t:t + CLOSE_REACH] = True
+    CLOSE[id(ref)] = (ref, close)
+    return ref
+
+
 def model_err(got, ref, dtype):
-    e = rel_err(got, ref)
+    """The largest row error; in bfloat16 over the rows that no close router call excuses (at least
+    half of them, and the excused rows stay within ten times the tolerance)."""
+    refd = ref.to(F).reshape(-1, ref.shape[-1])
+    rows = (got.to(F).cpu().reshape(refd.shape) - refd).pow(2).mean(-1).sqrt() / refd.pow(2).mean().sqrt().clamp_min(1e-30)
+    if dtype == "bfloat16" and id(ref) in CLOSE:
+        close = CLOSE[id(ref)][1]
+        assert int(close.sum()) * 2 <= close.numel() and float(rows.max()) < 10 * TOL[dtype]
+        rows = rows[~close]
+    e = float(rows.max())
     SEEN[dtype] = max(SEEN.get(dtype, 0.0), e)
     return e
 
@@ -142,7 +169,7 @@ def test_pair_embedding_and_the_token_it_remembers():
     assert rel_err(x, refs[2][:3]) < 1e-7
 
 
-@pytest.mark.parametrize("taps", [1, 2, 4])
+@pytest.mark.parametrize("taps", [1, 2, 4, 9])
 def test_convolution_over_time_carries_its_last_inputs(taps):
     g = torch.Generator().manual_seed(3)
     C, pad = 37, 5
@@ -192,12 +219,14 @@ def delta_reference(r, k, v, w, a, key_eps):
     return o
 
 
-@pytest.mark.parametrize("heads,dim,rank", [(1, 16, 3), (3, 24, 5), (2, 40, 8), (2, 64, 4), (1, 128, 16)])
-def test_delta_rule_kernels(heads, dim, rank):
+@pytest.mark.parametrize("heads,dim,rank,extra", [(1, 16, 3, 3), (3, 24, 5, 3), (2, 40, 8, 0), (2, 64, 4, 3), (2, 64, 4, 0),
+                                                  (1, 128, 16, 0), (1, 256, 8, 0), (2, 10, 2, 1), (3, 100, 4, 0)])
+def test_delta_rule_kernels(heads, dim, rank, extra):
+    """`extra` unused columns: rows of a multiple of four floats are copied in pieces of four."""
     g = torch.Generator().manual_seed(heads * 100 + dim)
     hk, scale, key_eps = heads * dim, 0.6, 1e-6
-    lens = (33, 1, 12)
-    projs = [torch.randn(n, 5 * hk + rank + 3, generator=g) for n in lens]          # r k v g a z1 and unused columns
+    lens = (90, 1, 12)                                   # the long one: more token groups than the kernel stages
+    projs = [torch.randn(n, 5 * hk + rank + extra, generator=g) for n in lens]          # r k v g a z1 and unused columns
     w2, w0, ab = (torch.randn(hk, rank, generator=g), torch.randn(hk, generator=g), torch.randn(hk, generator=g))
     refs = []
     for p in projs:
@@ -210,7 +239,7 @@ def test_delta_rule_kernels(heads, dim, rank):
     slots = [cache.open() for _ in lens]
     got = [[] for _ in lens]
     fed = [0, 0, 0]
-    for step in ([10, 1, 2], [1, 0, 1], [2, 0, 9], [20, 0, 0]):
+    for step in ([10, 1, 2], [1, 0, 1], [2, 0, 9], [77, 0, 0]):
         live = [i for i in (1, 2, 0) if step[i]]
         plan = plan_for(cache, [slots[i] for i in live], [step[i] for i in live])
         proj = torch.cat([projs[i][fed[i]:fed[i] + step[i]] for i in live]).cuda()
@@ -388,7 +417,7 @@ ONE_LAYER = {
 def test_each_mechanism_in_a_model_of_its_own(tmp_path, name, dtype):
     cfg, tensors = write_model(tmp_path / name, ONE_LAYER[name], seed=7)
     toks = tokens(cfg, 90, 3)
-    ref = pl.forward(cfg, tensors, toks)
+    ref = reference(cfg, tensors, toks)
     engine = sb.Engine(sb.load_model(tmp_path / name, dtype=dtype), max_tokens=256)
     assert model_err(run_cuts(engine, toks, [90]), ref, dtype) < TOL[dtype]
     assert model_err(run_cuts(engine, toks, [50] + [1] * 40), ref, dtype) < TOL[dtype]
@@ -431,7 +460,7 @@ def test_the_rank_of_the_decay_map_may_come_from_the_file(tmp_path):
 def test_whole_prompt_decoding_and_portions(folders, engines, name, dtype):
     _, cfg, tensors = folders[name]
     toks = tokens(cfg, 171, 5)
-    ref = pl.forward(cfg, tensors, toks)
+    ref = reference(cfg, tensors, toks)
     engine = engines(name, dtype)
     whole = run_cuts(engine, toks, [171])
     assert model_err(whole, ref, dtype) < TOL[dtype]
@@ -452,7 +481,7 @@ def test_unequal_batch_equals_each_alone_and_slots_are_reused(folders, engines, 
     from gpu_util import batch_unequal
     _, cfg, tensors = folders[name]
     reqs = [tokens(cfg, n, 10 + n) for n in (1, 70, 131, 23)]
-    refs = [pl.forward(cfg, tensors, r) for r in reqs]
+    refs = [reference(cfg, tensors, r) for r in reqs]
     engine = engines(name, dtype, max_tokens=512)
     # twice in the same engine: the second pass reuses the slots, pages and state rows of the first
     for _ in range(2):

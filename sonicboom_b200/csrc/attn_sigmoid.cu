@@ -143,7 +143,7 @@ template <int HD>
 constexpr int tc_smem() { return (TC_BM + 4 * KT) * (HD + 8) * 2; }
 
 template <int HD>
-__global__ void __launch_bounds__(TC_THREADS) attn_sigmoid_mma_kernel(const SigmoidParams p) {
+__global__ void __launch_bounds__(TC_THREADS, 2) attn_sigmoid_mma_kernel(const SigmoidParams p) {
   constexpr int LDS = HD + 8;          // shared-memory row stride: an odd number of 16-byte chunks
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t qs = (uint32_t)__cvta_generic_to_shared(smem);
@@ -198,12 +198,8 @@ __global__ void __launch_bounds__(TC_THREADS) attn_sigmoid_mma_kernel(const Sigm
   cp_async_wait<0>();
   __syncthreads();
 
-  uint32_t qf[HD / 16][4];
-#pragma unroll
-  for (int kk = 0; kk < HD / 16; ++kk) {
-    const int row = warp * 16 + (lane & 15), col = kk * 16 + (lane >> 4) * 8;
-    ldmatrix_x4(qs + (uint32_t)(row * LDS + col) * 2, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
-  }
+  // the query fragments are read from shared memory again for every tile: registers for two blocks an SM
+  const uint32_t q_frag = qs + (uint32_t)((warp * 16 + (lane & 15)) * LDS + (lane >> 4) * 8) * 2;
   const int ra = r_base + warp * 16 + (lane >> 2), rb = ra + 8;
   const int pos_a = ra < R ? pos0 + ra / G : -1, pos_b = rb < R ? pos0 + rb / G : -1;
   const float pb_a = p.head_bias && ra < R ? p.head_bias[kvh * G + ra % G] : 0.0f;
@@ -240,14 +236,16 @@ __global__ void __launch_bounds__(TC_THREADS) attn_sigmoid_mma_kernel(const Sigm
         for (int i = 0; i < 4; ++i) s[j][i] = 0.0f;
 #pragma unroll
       for (int kk = 0; kk < HD / 16; ++kk) {
+        uint32_t qf[4];
+        ldmatrix_x4(q_frag + kk * 32, qf[0], qf[1], qf[2], qf[3]);
 #pragma unroll
         for (int j = 0; j < KT / 16; ++j) {
           const int row = j * 16 + (lane & 7) + ((lane >> 4) << 3);
           const int col = kk * 16 + ((lane >> 3) & 1) * 8;
           uint32_t b0, b1, b2, b3;
           ldmatrix_x4(ks + (uint32_t)(row * LDS + col) * 2, b0, b1, b2, b3);
-          mma_bf16(s[2 * j], qf[kk], b0, b1);
-          mma_bf16(s[2 * j + 1], qf[kk], b2, b3);
+          mma_bf16(s[2 * j], qf, b0, b1);
+          mma_bf16(s[2 * j + 1], qf, b2, b3);
         }
       }
       const int t = lane & 3;
@@ -300,18 +298,18 @@ __global__ void __launch_bounds__(TC_THREADS) attn_sigmoid_mma_kernel(const Sigm
 // At most 16 rows for a sequence and key/value head (decoding): one block, whose tiles are two
 // pages (128 keys) wide; each of the 8 warps takes 16 keys of every tile for all rows, and the
 // warps' sums are added in warp order at the end.
-constexpr int DEC_ROWS = 16, DEC_KEYS = 2 * KT;
+constexpr int DEC_ROWS = 16, DEC_KEYS = 2 * KT, DEC_STAGES = 3;     // two tiles in flight beside the one in work
 template <int HD>
-constexpr int dec_smem() { return (DEC_ROWS + 4 * DEC_KEYS) * (HD + 8) * 2; }
+constexpr int dec_smem() { return (DEC_ROWS + DEC_STAGES * 2 * DEC_KEYS) * (HD + 8) * 2; }
 
 template <int HD>
 __global__ void __launch_bounds__(TC_THREADS) attn_sigmoid_mma_decode_kernel(const SigmoidParams p) {
   constexpr int LDS = HD + 8;
   static_assert(TC_THREADS / 32 * 16 == DEC_KEYS, "a warp for every 16 keys of a tile");
-  static_assert(TC_THREADS / 32 * DEC_ROWS * HD * 4 <= 4 * DEC_KEYS * LDS * 2, "the warps' sums fit the tiles' space");
+  static_assert(TC_THREADS / 32 * DEC_ROWS * HD * 4 <= DEC_STAGES * 2 * DEC_KEYS * LDS * 2, "the warps' sums fit the tiles' space");
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t qs = (uint32_t)__cvta_generic_to_shared(smem);
-  const uint32_t kv0 = qs + DEC_ROWS * LDS * 2;               // K0, V0, K1, V1 of 128 keys each
+  const uint32_t kv0 = qs + DEC_ROWS * LDS * 2;               // K and V of 128 keys for each stage
   sb_pdl_launch();
   sb_pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -351,9 +349,13 @@ __global__ void __launch_bounds__(TC_THREADS) attn_sigmoid_mma_decode_kernel(con
     cp_async16(qs + (uint32_t)(row * LDS + ch * 8) * 2,
                p.q + ((size_t)(row0 + t) * p.n_q_heads + kvh * G + g) * HD + ch * 8, valid);
   }
-  load_tile(0, 0);
-  cp_async_commit();
-  cp_async_wait<0>();
+  cp_async_commit();                                           // the query rows: a group of their own
+#pragma unroll
+  for (int st = 0; st < DEC_STAGES - 1; ++st) {
+    if (st < n_tiles) load_tile(st, st);
+    cp_async_commit();
+  }
+  cp_async_wait<DEC_STAGES - 1>();
   __syncthreads();
   uint32_t qf[HD / 16][4];
 #pragma unroll
@@ -373,16 +375,12 @@ __global__ void __launch_bounds__(TC_THREADS) attn_sigmoid_mma_decode_kernel(con
     for (int i = 0; i < 4; ++i) o[j][i] = 0.0f;
   const int krow0 = warp * 16;                                 // this warp's keys of every tile
   for (int it = 0; it < n_tiles; ++it) {
-    const int stage = it & 1;
+    const int stage = it % DEC_STAGES;
     const uint32_t ks = kv0 + stage * 2 * DEC_KEYS * LDS * 2, vs = ks + DEC_KEYS * LDS * 2;
-    if (it + 1 < n_tiles) {
-      load_tile(stage ^ 1, it + 1);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
+    cp_async_wait<DEC_STAGES - 2>();
+    __syncthreads();          // the tile has landed, and every warp is done with the stage that is filled next
+    if (it + DEC_STAGES - 1 < n_tiles) load_tile((it + DEC_STAGES - 1) % DEC_STAGES, it + DEC_STAGES - 1);
+    cp_async_commit();
     const int pi = 2 * it + krow0 / KT;
     if (pi < n_pages) {
       const int key0 = page_at(pi) * KT + krow0 % KT;
@@ -429,8 +427,9 @@ __global__ void __launch_bounds__(TC_THREADS) attn_sigmoid_mma_decode_kernel(con
         mma_bf16(o[2 * dj + 1], a, b2, b3);
       }
     }
-    __syncthreads();
   }
+  cp_async_wait<0>();
+  __syncthreads();
   // the warps' sums, added in warp order
   float* part = reinterpret_cast<float*>(smem + DEC_ROWS * LDS * 2);
   const int t4 = lane & 3;

@@ -248,11 +248,20 @@ delta_scan_kernel(const float* proj, int ld, int r_off, int k_off, int v_off, co
   }
 }
 
-template <int NPL, int VEC>
-cudaError_t launch_delta(dim3 grid, cudaStream_t stream, const float* proj, int ld, int r_off, int k_off, int v_off,
-                         const float* aux, const int32_t* seq_row0, const int32_t* seq_slot, int n_heads, int dim,
-                         float* state, float* out) {
-  constexpr int STAGES = NPL >= 16 ? 2 : 3;
+int delta_sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      n = 1;
+  }
+  return n;
+}
+
+template <int NPL, int VEC, int STAGES>
+cudaError_t launch_delta_staged(dim3 grid, cudaStream_t stream, const float* proj, int ld, int r_off, int k_off,
+                                int v_off, const float* aux, const int32_t* seq_row0, const int32_t* seq_slot,
+                                int n_heads, int dim, float* state, float* out) {
   constexpr size_t smem = (size_t)STAGES * TB * (5 * NPL * LPC + COLS) * sizeof(float);
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
@@ -263,6 +272,22 @@ cudaError_t launch_delta(dim3 grid, cudaStream_t stream, const float* proj, int 
   configured = true;
   return sb_launch<SB_K_OTHER>(delta_scan_kernel<NPL, VEC, STAGES>, grid, dim3(THREADS), smem, stream, proj, ld, r_off,
                                k_off, v_off, aux, seq_row0, seq_slot, n_heads, dim, state, out);
+}
+
+// Three stages of token groups; two where three would not fit an SM (the largest heads) or would
+// cost the grid a second wave of blocks.  The stages change when a token is copied, not a sum.
+template <int NPL, int VEC>
+cudaError_t launch_delta(dim3 grid, cudaStream_t stream, const float* proj, int ld, int r_off, int k_off, int v_off,
+                         const float* aux, const int32_t* seq_row0, const int32_t* seq_slot, int n_heads, int dim,
+                         float* state, float* out) {
+  constexpr size_t smem3 = (size_t)3 * TB * (5 * NPL * LPC + COLS) * sizeof(float);
+  const long per_sm = (long)((227 * 1024) / (smem3 + 1024));
+  const long blocks = (long)grid.x * grid.y * grid.z;
+  if (NPL < 16 && blocks <= (long)delta_sm_count() * (per_sm < 16 ? per_sm : 16))
+    return launch_delta_staged<NPL, VEC, (NPL < 16 ? 3 : 2)>(grid, stream, proj, ld, r_off, k_off, v_off, aux, seq_row0,
+                                                             seq_slot, n_heads, dim, state, out);
+  return launch_delta_staged<NPL, VEC, 2>(grid, stream, proj, ld, r_off, k_off, v_off, aux, seq_row0, seq_slot, n_heads, dim,
+                                          state, out);
 }
 
 }  // namespace

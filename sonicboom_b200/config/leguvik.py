@@ -22,7 +22,8 @@ config.json gives every size and every constant that may differ between models:
     mamba2:         heads, vdim, state, groups, norm_groups, conv (taps)
     general_delta:  heads, dim  (the rank of the decay's low-rank map is the shape of its first
                     matrix; `decay_rank` may state it, and must when weights are made at random)
-    attention:      heads, kv_heads, dim, vdim, scale, softcap, mask {size, keep_first}, and
+    attention:      heads, kv_heads, dim, vdim, scale, softcap (absent: none), mask {size, keep_first}
+                    (absent: every earlier key is seen), and
                     optionally kv_from: the layer whose keys and values this one reads
 
 What the design fixes is written into the part records by `to_spec`: the slope of the experts'
@@ -33,7 +34,7 @@ mixer ends in, and the tensor names (`l<i>.norm1`, `l<i>.canon1`, `l<i>.mix.in`,
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass
+from dataclasses import dataclass, replace
 from typing import Optional
 
 from .specs import (ConfigError, ConvSpec, FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec, NormSpec,
@@ -116,13 +117,13 @@ def _mixer(kind, m: dict, w: str):
         return DeltaRuleConfig(heads=_num(m, "heads", w), dim=_num(m, "dim", w),
                                decay_rank=None if rank is None else _num(m, "decay_rank", w))
     if kind == "attention":
-        mask = _sub(m, "mask", w)
+        mask = _sub(m, "mask", w) if m.get("mask") is not None else {}      # no mask: every earlier key is seen
         src = m.get("kv_from")
         a = SigmoidAttentionConfig(
             heads=_num(m, "heads", w), kv_heads=_num(m, "kv_heads", w), dim=_num(m, "dim", w),
             vdim=_num(m, "vdim", w), scale=_num(m, "scale", w, float),
             softcap=_num(m, "softcap", w, float, positive=False) if m.get("softcap") is not None else 0.0,
-            window=_num(mask, "size", w + "mask."),
+            window=_num(mask, "size", w + "mask.") if mask.get("size") is not None else 0,
             keep_first=_num(mask, "keep_first", w + "mask.", positive=False) if mask.get("keep_first") is not None else 0,
             kv_from=None if src is None else _num(m, "kv_from", w, positive=False))
         if a.heads % a.kv_heads:
@@ -130,7 +131,7 @@ def _mixer(kind, m: dict, w: str):
                               f"multiple of {a.kv_heads})")
         if a.softcap < 0 or a.keep_first < 0:
             raise ConfigError(f"missing/invalid config key: {w}softcap / {w}mask.keep_first (must be >= 0)")
-        return a
+        return a if a.window else replace(a, keep_first=0)         # without a window every key is in sight anyway
     raise ConfigError(f"unsupported config key: {w[:-6]}type = {kind!r} (mamba2, general_delta or attention)")
 
 
@@ -216,7 +217,9 @@ class LeguvikConfig:
                     mixer["decay_rank"] = m.decay_rank
             else:
                 mixer = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "scale": m.scale,
-                         "softcap": m.softcap, "mask": {"size": m.window, "keep_first": m.keep_first}}
+                         "softcap": m.softcap}
+                if m.window:
+                    mixer["mask"] = {"size": m.window, "keep_first": m.keep_first}
                 if m.kv_from is not None:
                     mixer["kv_from"] = m.kv_from
             mlp = None

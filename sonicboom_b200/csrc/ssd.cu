@@ -34,13 +34,14 @@ __device__ __forceinline__ float softplus(float x) { return fmaxf(x, 0.0f) + log
 
 template <typename TW>
 __global__ void ssd_prep_kernel(const float* proj, int ld_proj, int dt_off, float* xbc, int ld, int x_off, int xdt_off,
-                                int n_heads, int vdim, const TW* __restrict__ dt_bias, const TW* __restrict__ a_log,
-                                float* decay) {
+                                int n_heads, int vdim, int per, const TW* __restrict__ dt_bias,
+                                const TW* __restrict__ a_log, float* decay) {
   sb_pdl_launch();
   sb_pdl_wait();
   const size_t r = blockIdx.x;
   const int inner = n_heads * vdim;
-  for (int c = threadIdx.x; c < inner; c += blockDim.x) {
+  // a thread takes `per` channels, a block's apart: one at few rows, where the blocks are few
+  for (int i = 0, c = blockIdx.y * blockDim.x * per + threadIdx.x; i < per && c < inner; ++i, c += blockDim.x) {
     const int h = c / vdim;
     const float dt = softplus(proj[r * ld_proj + dt_off + h] + sb_to_f32<TW>(dt_bias[h]));
     xbc[r * ld + xdt_off + c] = dt * xbc[r * ld + x_off + c];
@@ -87,9 +88,12 @@ extern "C" int sb_ssd_prep(const float* proj, int n_rows, int ld_proj, int dt_of
       (x_off < xdt_off + inner && xdt_off < x_off + inner))
     SB_FAIL(SB_ERR_ARG, "sb_ssd_prep: offsets %d of %d; %d, %d of %d", dt_off, ld_proj, x_off, xdt_off, ld);
   if (!sb_valid_dtype(w_dtype)) SB_FAIL(SB_ERR_ARG, "sb_ssd_prep: dtype code %d", w_dtype);
+  const int per = n_rows >= 256 ? 8 : 1;
+  const int by = (inner + 256 * per - 1) / (256 * per);
+  if (by > 65535) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_ssd_prep: %d values a row", inner);
   SB_DISPATCH_DTYPE(w_dtype, TW, {
-    sb_launch<SB_K_ELEMENTWISE>(ssd_prep_kernel<TW>, dim3(n_rows), dim3(256), 0, stream, proj, ld_proj, dt_off, xbc, ld,
-                                x_off, xdt_off, n_heads, vdim, (const TW*)dt_bias, (const TW*)a_log, decay);
+    sb_launch<SB_K_ELEMENTWISE>(ssd_prep_kernel<TW>, dim3(n_rows, by), dim3(256), 0, stream, proj, ld_proj, dt_off, xbc, ld,
+                                x_off, xdt_off, n_heads, vdim, per, (const TW*)dt_bias, (const TW*)a_log, decay);
   });
   SB_CHECK_LAUNCH("sb_ssd_prep");
   return SB_OK;

@@ -14,8 +14,9 @@ import torch
 
 def attention(heads, kv_heads, dim, vdim, window, keep_first=0, scale=None, softcap=0.0, kv_from=None):
     m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
-         "scale": scale if scale is not None else dim ** -0.5, "softcap": softcap,
-         "mask": {"size": window, "keep_first": keep_first}}
+         "scale": scale if scale is not None else dim ** -0.5, "softcap": softcap}
+    if window:                                               # window 0: config.json has no mask
+        m["mask"] = {"size": window, "keep_first": keep_first}
     if kv_from is not None:
         m["kv_from"] = kv_from
     return m

@@ -121,7 +121,8 @@ def sigmoid_attention(h, get, m, keys=None, values=None):
     cap, pb = m.get("softcap", 0.0), get("pb")
     out = torch.zeros(T, H, V, dtype=F)
     for i in range(T):
-        seen = [j for j in range(T) if visible(i, j, m["mask"]["size"], m["mask"].get("keep_first", 0))]
+        mask = m.get("mask") or {"size": T}                     # no mask: every earlier key
+        seen = [j for j in range(T) if visible(i, j, mask["size"], mask.get("keep_first", 0))]
         for hh in range(H):
             g = hh // (H // G)
             s = (keys[seen, g] @ q[i, hh]) * m["scale"]

@@ -397,6 +397,7 @@ ONE_LAYER = {
     "attention": model(64, 32, [layer("attention", attention(2, 1, 16, 16, window=11, keep_first=4, softcap=3.0))],
                        taps=0, bigram=None),
     "attention_wide_values": model(64, 32, [layer("attention", attention(3, 3, 8, 40, window=200))], taps=0),
+    "attention_without_a_mask": model(64, 32, [layer("attention", attention(2, 1, 64, 64, window=0, softcap=4.0))], taps=2),
     "attention_shared_keys": model(64, 32, [layer("attention", attention(4, 2, 32, 16, window=30, keep_first=2)),
                                             layer("attention", attention(4, 2, 32, 16, window=8, keep_first=12,
                                                                          scale=0.4, softcap=8.0, kv_from=0))], taps=0),

@@ -55,6 +55,10 @@ def test_what_config_json_leaves_out_does_not_exist():
     assert c.canon_taps == 0 and c.bigram is None and c.logit_softcap == 0.0
     names = {r.name for r in tensor_requests(spec)}
     assert not any("canon" in n or n == "bigram" or ".mlp." in n for n in names)
+    open_ = model(50, 32, [layer("attention", attention(2, 1, 8, 8, window=0))])
+    c, _ = spec_from_config_dict(open_)
+    assert c.layers[0].mixer.window == 0 and "mask" not in c.to_dict()["layers"][0]["mixer"]
+    assert LeguvikConfig.from_dict(c.to_dict()) == c
 
 
 @pytest.mark.parametrize("path,value,match", [

@@ -922,12 +922,12 @@ def leguvik_kernels(bench, z, rows, context):
     # experts
     E, top, eff = z["experts"], z["top"], z["expert_ff"]
     h = torch.randn(rows, W, device=dev).to(bf)
-    logits = torch.randn(rows, E, device=dev)
+    logits = torch.randn(rows, E, generator=bench.gen).to(dev)          # seeded: the same experts are hit every run
     ids, wts = torch.empty(rows, top, dtype=torch.int32, device=dev), torch.empty(rows, top, device=dev)
     rec("moe_route", timed(lambda: ops.moe_route(logits, top, ids, wts)), rows * (E * 4 + top * 8))
     w_up = torch.randn(E, 2, eff, W, device=dev).to(bf) * 0.02
     w_down = torch.randn(E, W, eff, device=dev).to(bf) * 0.02
-    used = min(E, rows * top)
+    used = int(torch.unique(ids).numel())                # experts that some row chose: their weights are what must be read
     moe_bytes = used * 3 * eff * W * 2 + rows * W * 10 + rows * top * (eff * 4 + W * 8)
     moe_flops = 6 * rows * top * eff * W
     rec(f"moe_experts: group, up, down, combine ({E} experts of {eff}, {top} a row)",

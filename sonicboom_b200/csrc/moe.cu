@@ -301,6 +301,8 @@ moe_gemm_mma_kernel(const bf16* a, const bf16* __restrict__ w, const int32_t* or
     for (int j = 0; j < 4; ++j)
 #pragma unroll
       for (int r = 0; r < 4; ++r) acc[i][j][r] = 0.0f;
+  // whether any of this warp's rows holds a pair (the upper half of a ragged tile's warps often has none)
+  const int mi_n = cnt > warp_m * (MI * 16) ? 1 : 0;
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
     if (s < n_k) load_stage(s, s);
@@ -312,6 +314,7 @@ moe_gemm_mma_kernel(const bf16* a, const bf16* __restrict__ w, const int32_t* or
     if (kt + STAGES - 1 < n_k) load_stage((kt + STAGES - 1) % STAGES, kt + STAGES - 1);
     cp_async_commit();
     const uint32_t a_base = smem_base + (kt % STAGES) * (A_BYTES + B_BYTES), b_base = a_base + A_BYTES;
+    if (mi_n == 0) continue;                       // none of the warp's rows holds a pair: it only copies
 #pragma unroll
     for (int ks = 0; ks < TK / 16; ++ks) {
       uint32_t af[MI][4], bfr[4][2];

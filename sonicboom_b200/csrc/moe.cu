@@ -7,7 +7,7 @@
 //   sb_moe_up:      for every tile, gate and up products of the expert with the clamped gated
 //                   activation a * sigmoid(slope a) * (b + 1) in the epilogue.  bfloat16 with inner
 //                   sizes in multiples of 8 runs on tensor cores (mma.sync m16n8k16, tiles of 64 or
-//                   128 pairs x 128 weight rows x 64 inner values, a 3-stage cp.async pipeline whose
+//                   128 pairs x 128 weight rows x 64 inner values, a cp.async pipeline of 3 or 4 stages whose
 //                   16-byte copies also stream an expert's weights when a step has few pairs); the
 //                   rest runs the plain float32 tiles of 32 pairs
 //   sb_moe_down:    for every tile, the expert's down product, one float32 row per pair
@@ -201,7 +201,10 @@ moe_gemm_kernel(const TA* a, const TW* __restrict__ w, const int32_t* order, con
 
 // ------------------------------------------------------------------------------ tensor cores
 typedef __nv_bfloat16 bf16;
-constexpr int TN = 128, TK = 64, STAGES = 3, MMA_THREADS = 256;   // weight rows, inner values of a tile
+constexpr int TN = 128, TK = 64, MMA_THREADS = 256;   // weight rows, inner values of a tile
+// cp.async stages: four for the tiles of 64 pairs (24 KiB a stage, two blocks an SM), which also stream an
+// expert's weights when a step has few pairs; three for the tiles of 128 pairs (32 KiB a stage)
+constexpr int stages_for(int mi) { return mi <= 2 ? 4 : 3; }
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -230,7 +233,7 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
   return (uint32_t)(row * (TK * 2) + ((chunk ^ (row & 7)) << 4));
 }
 
-constexpr int mma_smem(int mi) { return STAGES * (mi * 32 + TN) * TK * 2; }
+constexpr int mma_smem(int mi) { return stages_for(mi) * (mi * 32 + TN) * TK * 2; }
 
 // One tile of up to MI * 32 pairs of one expert.  2 x 4 warps, MI * 16 pairs x 32 weight rows each.
 // GATED: the 128 weight rows of a block are, for each of its four warp columns, 16 gate rows and
@@ -241,7 +244,7 @@ template <int MI, bool GATED>
 __global__ void __launch_bounds__(MMA_THREADS, 2)
 moe_gemm_mma_kernel(const bf16* a, const bf16* __restrict__ w, const int32_t* order, const int32_t* meta, int top,
                     int n_out, int n_in, float limit, float slope, void* out_) {
-  constexpr int TM = MI * 32;
+  constexpr int TM = MI * 32, STAGES = stages_for(MI);
   constexpr int A_BYTES = TM * TK * 2, B_BYTES = TN * TK * 2;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int32_t src_row[TM];

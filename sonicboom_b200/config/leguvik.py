@@ -1,6 +1,7 @@
 """Typed configuration of the Leguvik decoder, read from its own config.json keys.
 
-A Leguvik model is a list of pre-norm layers, x <- x + mixer(norm1(x)), x <- x + ff(norm2(x)), whose
+A Leguvik model is a list of layers in which a norm comes before each sublayer and the sublayer's
+result joins the stream (x1 = x + mix(n1(x)); x2 = x1 + ffn(n2(x1))), whose
 norms are layer norms with a weight and no bias.  What each sublayer reads passes a short causal
 convolution over time first (h <- h + conv(h)).  A token's embedding is its own row plus a row of
 a second table chosen by a hash of the previous and the current token.  A layer's mixer is a

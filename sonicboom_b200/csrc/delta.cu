@@ -3,7 +3,7 @@
 //
 //     S_t = diag(w_t) S_(t-1) - (a_t * u_t) (u_t^T S_(t-1)) + k_t v_t^T,      o_t = S_t^T r_t,
 //
-// per head, u = k / sqrt(sum(k^2) + key_eps), both products reading the old state.  Column j of S
+// per head, u = k / sqrt(sum(k^2) + key_eps); decay and removal act on S_(t-1), then k v^T is added.  Column j of S
 // (the `dim` values of one value channel) obeys  s <- w * s - (a * u) (u . s) + k v_j,  o_j = s . r,
 // so columns are independent.
 //

@@ -3,11 +3,11 @@ removal along the unit key,
 
     S_t = diag(w_t) S_(t-1) - (a_t * u_t) (u_t^T S_(t-1)) + k_t v_t^T,      o_t = S_t^T r_t
 
-per head, S_0 = 0, both products reading the old state; r, k, v of `head_dim` values per head,
+per head, S_0 = 0; decay and removal act on S_(t-1), then k v^T is added; r, k, v of `head_dim` values per head,
 u = k / sqrt(sum(k^2) + key_eps) the head's unit key, decays w = exp(-decay_scale * sigmoid(W2
-tanh(W1 h) + w0)) and removal rates a = sigmoid(A h + b) per head and key channel.  Every head's o
-is divided by its root mean square (`eps`); the heads are concatenated, multiplied by a weight of
-all heads' size and by sigmoid(G h), and projected by O.
+tanh(W1 h) + w0)) and removal rates a = sigmoid(A h + b) per head and key channel.  Output: an RMS
+norm of o within each head (`eps`), a channel-wise weight vector that spans all heads, the gate
+sigmoid(G h), then the product with O.
 
 r, k, v, g, the removal logits and the first half of the decay map are one product; the map's
 second half, decays, rates, the unit key, the state and the recurrence are float32 whatever the

@@ -153,9 +153,10 @@ class PolyNormFF(FeedForward):
 @register_feed_forward("experts_glu_clamped")
 class ExpertsClampedGLU(FeedForward):
     """Mixture of experts over clamped gated feed-forwards (the form of `glu_clamped`): router logits
-    z = R h + b in float32; each token goes through the `top` experts with the largest logits (the
-    lower index wins a tie), weighted by the softmax over the chosen logits only; a shared expert
-    (`shared`, a feed-forward spec of its own, or None) runs for every token and is added.
+    z = R h + b in float32; a token is sent to its `top` experts of largest logit (ties go to the
+    lower index) and their results are mixed with exp(z_e) normalised among those `top` alone; an
+    always-on expert (`shared`, a feed-forward spec of its own, or None) contributes to every
+    token's result unweighted.
     `params`: `experts`, `top`, `limit`, `slope`, `shared`.  Tensors after the prefix: router
     [experts, width], router.b [experts], e<j>.gate, e<j>.up [intermediate, width], e<j>.down [width,
     intermediate]; the shared expert's under its own prefix.

@@ -26,6 +26,7 @@ CORE = {
     "sb_abi_version": ("i", ""),
     "sb_embed": ("i", "pipiiifps"),
     "sb_rmsnorm": ("i", "ppiipifpis"),
+    "sb_rmsnorm_ld": ("i", "pipiipifpis"),
     "sb_softcap": ("i", "pzfs"),
     "sb_add_bias": ("i", "ppiiis"),
     "sb_cast": ("i", "pipizs"),
@@ -46,15 +47,17 @@ CORE = {
     "sb_norm_add": ("i", "ppiipifppifpis"),
     "sb_depth_mix": ("i", "pzipiiippifpipppifs"),
     "sb_glu_clamped": ("i", "piiffipis"),
-    "sb_latent_prep": ("i", "piiiiiipppppipifpipiiis"),
+    "sb_gated_act": ("i", "piiiffipis"),
+    "sb_scale": ("i", "pzfs"),
+    "sb_latent_prep": ("i", "piiiiiipppppipifpipiiipiifs"),
     "sb_head_linear": ("i", "pizzpiiiiipizzs"),
     "sb_mlstm_scan": ("i", "pippiiippiffipipps"),
     "sb_mlstm_out": ("i", "pppiiiipifpis"),
-    "sb_attention_plain": ("i", "ppiippppipiiiiifps"),
+    "sb_attention_plain": ("i", "ppiippppipiiiiifpfs"),
     "sb_stream_add": ("i", "pppiiippifpis"),
     "sb_polynorm": ("i", "piipifpis"),
-    "sb_attn_prep": ("i", "piiiiiiiiiiiippppifppppipipiis"),
-    "sb_attn_unrotate": ("i", "ppiiiiiipps"),
+    "sb_attn_prep": ("i", "piiiiiiiiiiiippppiiffppppipipiis"),
+    "sb_attn_unrotate": ("i", "ppiiiiiipppis"),
     "sb_linrec_prep": ("i", "piiiiiiffiipppfppiiis"),
     "sb_linrec_scan": ("i", "piiiipppiippiiipps"),
     "sb_linrec_force_columns": ("v", "i"),
@@ -69,6 +72,7 @@ CORE = {
     "sb_ssd_out": ("i", "ppiiipiiiiippifpis"),
     "sb_attention_sigmoid": ("i", "ppiippiippppipiiiiiiffps"),
     "sb_moe_route": ("i", "piiipps"),
+    "sb_moe_route_scored": ("i", "ppiiiiiifipps"),
     "sb_moe_tile_rows": ("i", "iiiii"),
     "sb_moe_max_tiles": ("i", "iii"),
     "sb_moe_group": ("i", "piiipps"),
@@ -87,7 +91,7 @@ ATTENTION = {
     "sb_attention_status": ("i", ""),
     "sb_attention_last_launches": ("i", ""),
     "sb_attention_scratch_bytes": ("z", "iiiii"),
-    "sb_attention": ("i", "ppiiippppipiiiifpzpiiiipzps"),
+    "sb_attention": ("i", "ppiiippppipiiiifpzpiiiipzpfs"),
     "sb_attention_decode_static": ("i", "ppiiippppipiiiifis"),
     "sb_attention_static_scratch_bytes": ("z", ""),
 }

@@ -7,13 +7,15 @@ from .qwen2 import Qwen2Config
 from .zolulix import ZolulixConfig
 from .mefupel import MefupelConfig
 from .leguvik import LeguvikConfig
+from .bulodra import BulodraConfig
 
 register_architecture("Qwen2ForCausalLM", Qwen2Config.from_dict, Qwen2Config.to_spec)
 register_architecture("Zolulix", ZolulixConfig.from_dict, ZolulixConfig.to_spec)
 register_architecture("Mefupel", MefupelConfig.from_dict, MefupelConfig.to_spec)
 register_architecture("Leguvik", LeguvikConfig.from_dict, LeguvikConfig.to_spec)
+register_architecture("Bulodra", BulodraConfig.from_dict, BulodraConfig.to_spec)
 
-__all__ = ["ConfigError", "ConvSpec", "PairEmbeddingSpec", "DepthMixSpec", "ZolulixConfig", "MefupelConfig", "LeguvikConfig", "StreamInjection", "FeedForwardSpec", "LayerSpec", "MixerSpec", "ModelSpec", "NormSpec",
+__all__ = ["ConfigError", "ConvSpec", "PairEmbeddingSpec", "DepthMixSpec", "ZolulixConfig", "MefupelConfig", "LeguvikConfig", "BulodraConfig", "StreamInjection", "FeedForwardSpec", "LayerSpec", "MixerSpec", "ModelSpec", "NormSpec",
            "PositionSpec", "ScheduleEntry", "ARCHITECTURES", "Architecture", "architecture_name",
            "lookup", "read_config_json", "register_architecture", "spec_from_config_dict",
            "Qwen2Config"]

@@ -24,6 +24,7 @@ class PositionSpec:
     head_dim: int
     theta: float = 10000.0
     rotary_dim: int = 0            # 0 = the whole head is rotated
+    params: tuple = ()             # extra (key, value) pairs for kinds that scale their frequencies
 
 
 @dataclass(frozen=True)
@@ -98,7 +99,7 @@ class LayerSpec:
     block without a feed-forward has `feed_forward` (and its norms) None."""
     arrangement: str               # key of parts.BLOCKS, e.g. "pre_norm"
     mixer: MixerSpec
-    mixer_norm: NormSpec
+    mixer_norm: Optional[NormSpec]                 # None: the arrangement has no norm before the mixer
     feed_forward: Optional[FeedForwardSpec]
     feed_forward_norm: Optional[NormSpec]
     mixer_post_norm: Optional[NormSpec] = None
@@ -106,6 +107,7 @@ class LayerSpec:
     depth_mix: Optional[DepthMixSpec] = None
     mixer_conv: Optional[ConvSpec] = None          # on the mixer's input, after its norm
     feed_forward_conv: Optional[ConvSpec] = None   # on the feed-forward's input, after its norm
+    params: tuple = ()             # extra (key, value) pairs for arrangements with constants of their own
 
     @property
     def kind(self) -> str:
@@ -146,6 +148,7 @@ class ModelSpec:
     stop_tokens: tuple = ()
     embedding_scale: float = 1.0        # multiplies every embedding row (1: as stored)
     logit_cap: float = 0.0              # c > 0: logits = c * tanh(logits / c); 0: no cap
+    logit_scale: float = 1.0            # multiplies the head's product (before a cap)
     injections: tuple = ()              # of StreamInjection, at most one per schedule entry
     unused_tensors: tuple = ()          # (name, shape) of tensors a file may hold that nothing reads
     pair_embedding: Optional[PairEmbeddingSpec] = None   # added to every embedding row
@@ -155,6 +158,8 @@ class ModelSpec:
             raise ConfigError("model has no layers")
         if not self.embedding_scale > 0.0:
             raise ConfigError(f"embedding_scale {self.embedding_scale} must be positive")
+        if not self.logit_scale > 0.0:
+            raise ConfigError(f"logit_scale {self.logit_scale} must be positive")
         if self.logit_cap < 0.0:
             raise ConfigError(f"logit_cap {self.logit_cap} must be zero (none) or positive")
         seen = set()

@@ -87,7 +87,7 @@ __device__ __forceinline__ uint32_t dt_addr(uint32_t tile, int row, int chunk) {
 // One warp's 32 keys (rows key_row0 ... + 31 of the tile) for its 16 query rows.
 __device__ __forceinline__ void dt_tile_step(uint32_t qs, uint32_t ks, uint32_t vs,
                                              int key_row0, int key0, int pos_a, int pos_b, int window,
-                                             float scale_log2, float (&m)[2], float (&l)[2],
+                                             const ScoreMap sm, float (&m)[2], float (&l)[2],
                                              float (&o)[HD / 8][4], int lane) {
   float s[4][4];
 #pragma unroll
@@ -118,7 +118,7 @@ __device__ __forceinline__ void dt_tile_step(uint32_t qs, uint32_t ks, uint32_t 
       const int key = key0 + j * 8 + 2 * t + (i & 1);
       const int pos = (i < 2) ? pos_a : pos_b;
       const bool seen = key <= pos && (window == 0 || pos - key < window);
-      const float v = seen ? s[j][i] * scale_log2 : -INFINITY;
+      const float v = seen ? mapped_score(s[j][i], sm) : -INFINITY;
       s[j][i] = v;
       tmax[i >> 1] = fmaxf(tmax[i >> 1], v);
     }
@@ -503,7 +503,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const AttnPar
         }
         const uint32_t ks = ring + s * DT_STAGE_BYTES, vs = ks + DT_TILE_BYTES;
         dt_tile_step(qs, ks, vs, half * 32, (w.tile_lo + j) * KT + half * 32, pos_a, pos_b, p.window,
-                     p.scale_log2, m, l, o, lane);
+                     score_map(p), m, l, o, lane);
         if (j + 1 < w.n_tiles) {                       // the last tile's stage stays for the merge
           __syncwarp();
           if (lane == 0) mbar_arrive(empty0 + 8 * s);

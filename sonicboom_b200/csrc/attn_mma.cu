@@ -66,10 +66,25 @@ struct AttnParams {
   int n_q_heads, n_kv_heads, window, n_splits;
   int n_seqs;
   float scale_log2;            // scale * log2(e)
+  float cap_a, cap_b;          // a score cap c > 0: cap_a = 2 scale / c, cap_b = c log2(e); else both 0
   const float* sink;           // [n_q_heads] or null: exp(sink) joins each row's softmax denominator
   const char* warm;            // decode: bytes the next kernel will read, asked into L2 (or null)
   size_t warm_bytes;
 };
+
+// A raw dot product to the exponent's argument: score * log2(e) with score = dot * scale, or, with
+// a cap c, score = c tanh(dot * scale / c) written as c (1 - 2 / (exp(2 dot scale / c) + 1)).
+// Monotone in the dot product, so the largest dot product gives the largest result.
+struct ScoreMap {
+  float scale_log2, cap_a, cap_b;
+};
+__device__ __forceinline__ float mapped_score(float dot, const ScoreMap& sm) {
+  return sm.cap_b != 0.0f ? sm.cap_b * (1.0f - __fdividef(2.0f, __expf(dot * sm.cap_a) + 1.0f))
+                          : dot * sm.scale_log2;
+}
+__device__ __forceinline__ ScoreMap score_map(const AttnParams& p) {
+  return ScoreMap{p.scale_log2, p.cap_a, p.cap_b};
+}
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
                                          uint32_t b1) {
@@ -123,7 +138,7 @@ __device__ __forceinline__ void load_kv_tile(uint32_t ks, uint32_t vs, const bf1
 template <int NKEYS>
 __device__ __forceinline__ void tile_step(const uint32_t (&qf)[HD / 16][4], uint32_t ks,
                                           uint32_t vs, int key0, int pos_a, int pos_b, int window,
-                                          float scale_log2, float (&m)[2], float (&l)[2],
+                                          const ScoreMap sm, float (&m)[2], float (&l)[2],
                                           float (&o)[HD / 8][4], int lane) {
   float s[NKEYS / 8][4];
 #pragma unroll
@@ -151,7 +166,7 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[HD / 16][4], uint
       const int key = key0 + j * 8 + 2 * t + (i & 1);
       const int pos = (i < 2) ? pos_a : pos_b;
       const bool seen = key <= pos && (window == 0 || pos - key < window);
-      const float v = seen ? s[j][i] * scale_log2 : -INFINITY;
+      const float v = seen ? mapped_score(s[j][i], sm) : -INFINITY;
       s[j][i] = v;
       tmax[i >> 1] = fmaxf(tmax[i >> 1], v);
     }
@@ -282,7 +297,7 @@ __global__ void __launch_bounds__(PREFILL_THREADS) attn_prefill_kernel(const Att
       cp_async_wait<0>();
     }
     __syncthreads();
-    tile_step<KT>(qf, ks, vs, tile * KT, pos_a, pos_b, p.window, p.scale_log2, m, l, o, lane);
+    tile_step<KT>(qf, ks, vs, tile * KT, pos_a, pos_b, p.window, score_map(p), m, l, o, lane);
     __syncthreads();
   }
 
@@ -415,7 +430,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
     if (tile == tile_lo) load_q_frags(qs, 0, lane, qf);
     // this warp's 16 keys of the tile
     const uint32_t off = (uint32_t)(warp * 16 * LDS) * 2;
-    tile_step<16>(qf, ks + off, vs + off, tile * KT + warp * 16, pos_a, pos_b, p.window, p.scale_log2,
+    tile_step<16>(qf, ks + off, vs + off, tile * KT + warp * 16, pos_a, pos_b, p.window, score_map(p),
                   m, l, o, lane);
     __syncthreads();                                  // the stage is free: request a later tile into it
     if (tile + STAGES <= tile_hi) {
@@ -661,7 +676,7 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
                             const void* cache, int n_q_heads, int n_kv_heads, int hd, int window,
                             float scale, void* scratch, size_t scratch_bytes, int* counters,
                             int n_counters, int max_len, int n_pages, int n_sms,
-                            const void* warm, size_t warm_bytes, const float* sink,
+                            const void* warm, size_t warm_bytes, const float* sink, float softcap,
                             cudaStream_t stream) {
   if (hd != HD) SB_FAIL(SB_ERR_ARG, "sb_attention: built for head size %d, called with %d", HD, hd);
   if (page_size != KT)
@@ -684,6 +699,9 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
   p.cache = (const bf16*)cache; p.scratch = (float*)scratch; p.counters = counters;
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.n_seqs = n_seqs;
   p.scale_log2 = scale * LOG2E;
+  if (softcap < 0.0f) SB_FAIL(SB_ERR_ARG, "sb_attention: score cap %g (0: none)", softcap);
+  p.cap_a = softcap > 0.0f ? 2.0f * scale / softcap : 0.0f;
+  p.cap_b = softcap > 0.0f ? softcap * LOG2E : 0.0f;
   const int G = n_q_heads / n_kv_heads;
   static bool configured = false;
   if (!configured) {
@@ -928,6 +946,7 @@ extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, 
   p.n_seqs = n_seqs;
   p.sink = nullptr;
   p.scale_log2 = scale * LOG2E;
+  p.cap_a = p.cap_b = 0.0f;
   sb_launch<SB_K_ATTENTION>(attn_decode_kernel<DEC_STAGES>, dim3(n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32), DECODE_SMEM,
             stream, p);
   SB_CHECK_LAUNCH("sb_attention_decode_static (decode)");

@@ -5,7 +5,8 @@
 // For the query at absolute position i: key j is visible when j <= i and (window == 0 or
 // i < j + window); s_j = (q . k_j) * scale with the scale applied after the whole dot;
 // out = sum(exp(s_j - m) v_j) / sum(exp(s_j - m)) (core/src/nn/attention.cpp:26-105,
-// 121-183).  With `sink` (one float32 per query head) the denominator also holds exp(sink_h).  Keys are taken in chunks whose boundaries are absolute multiples of the chunk
+// 121-183).  With `sink` (one float32 per query head) the denominator also holds exp(sink_h);
+// with a cap c > 0 the score is c tanh(s_j / c).  Keys are taken in chunks whose boundaries are absolute multiples of the chunk
 // length and merged in ascending order, as the reference's split decode attention does
 // (core/src/model/emit.cpp:538-544, core/src/nn/cuda_elementwise.cu:886-897), so the sum
 // depends only on the positions, not on the batch or on where the pages lie.
@@ -24,7 +25,7 @@ __global__ void __launch_bounds__(THREADS)
 attn_plain_kernel(const TQ* q, TQ* out, const int32_t* row_seq, const int32_t* row_pos,
                   const int32_t* page_off, const int32_t* page_ids, int page_size,
                   const TC* cache, int n_q_heads, int n_kv_heads,
-                  int hd, int window, float scale, const float* __restrict__ sink) {
+                  int hd, int window, float scale, const float* __restrict__ sink, float softcap) {
   __shared__ float qs[MAX_HD];
   __shared__ float scores[CHUNK];
   __shared__ float bcast[3];
@@ -61,6 +62,7 @@ attn_plain_kernel(const TQ* q, TQ* out, const int32_t* row_seq, const int32_t* r
         float dot = 0.0f;
         for (int d = lane; d < hd; d += 32) dot = fmaf(qs[d], sb_to_f32<TC>(krow[d]), dot);
         s = sb_warp_sum(dot) * scale;
+        if (softcap > 0.0f) s = softcap * tanhf(s / softcap);
       }
       if (lane == 0) scores[j - cs] = s;
     }
@@ -136,7 +138,8 @@ extern "C" int sb_attention_plain(const void* q, void* out, int act_dtype, int n
                                   const int32_t* page_off, const int32_t* page_ids, int page_size,
                                   const void* cache, int cache_dtype, int n_q_heads,
                                   int n_kv_heads, int hd, int window, float scale,
-                                  const float* sink, cudaStream_t stream) {
+                                  const float* sink, float softcap, cudaStream_t stream) {
+  if (softcap < 0.0f) SB_FAIL(SB_ERR_ARG, "sb_attention_plain: score cap %g (0: none)", softcap);
   if (int rc = sb_check_attention_args("sb_attention_plain", n_rows, n_q_heads, n_kv_heads, hd,
                                        window, page_size))
     return rc;
@@ -150,7 +153,7 @@ extern "C" int sb_attention_plain(const void* q, void* out, int act_dtype, int n
     SB_DISPATCH_DTYPE(cache_dtype, TC, {
       sb_launch(attn_plain_kernel<TQ, TC>, grid, dim3(THREADS), 0, stream,
           (const TQ*)q, (TQ*)out, row_seq, row_pos, page_off, page_ids, page_size,
-          (const TC*)cache, n_q_heads, n_kv_heads, hd, window, scale, sink);
+          (const TC*)cache, n_q_heads, n_kv_heads, hd, window, scale, sink, softcap);
     });
   });
   SB_CHECK_LAUNCH("sb_attention_plain");

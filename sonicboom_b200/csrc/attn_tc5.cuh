@@ -311,6 +311,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const AttnPa
     const int p_hi = rq_base < R ? pos0 + min(R - 1, rq_base + T5_ROWS - 1) / G : 0x7fffffff;
     const uint32_t o_addr = t_base + 2 * KT;
     float m_ref = -INFINITY, l = 0.0f;      // reference maximum (log2 domain) and row sum
+    const ScoreMap sm = score_map(p);
+    const bool capped = sm.cap_b != 0.0f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int s = j & 1, use = j >> 1, key0 = (tile_lo + j) * KT;
@@ -339,7 +341,9 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const AttnPa
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int i = 0; i < KT; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(sv[i]));
-      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;   // scale > 0
+      // scale > 0 and the cap is monotone: the largest dot product gives the largest exponent
+      const float mx_all = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      const float m_tile = capped ? (mx_all == -INFINITY ? -INFINITY : mapped_score(mx_all, sm)) : mx_all * p.scale_log2;
       if (__any_sync(0xffffffffu, m_tile > m_ref + T5_LAZY || (m_ref == -INFINITY && m_tile > m_ref))) {
         // move this warp's references to the rows' current maxima
         const float m_new = fmaxf(m_ref, m_tile);
@@ -356,8 +360,11 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const AttnPa
       float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
       for (int i = 0; i < KT; i += 2) {
-        const float p0 = t5_ex2(fmaf(__uint_as_float(sv[i]), p.scale_log2, -base));
-        const float p1 = t5_ex2(fmaf(__uint_as_float(sv[i + 1]), p.scale_log2, -base));
+        const float d0 = __uint_as_float(sv[i]), d1 = __uint_as_float(sv[i + 1]);
+        const float p0 = capped ? (d0 == -INFINITY ? 0.0f : t5_ex2(mapped_score(d0, sm) - base))
+                                : t5_ex2(fmaf(d0, p.scale_log2, -base));
+        const float p1 = capped ? (d1 == -INFINITY ? 0.0f : t5_ex2(mapped_score(d1, sm) - base))
+                                : t5_ex2(fmaf(d1, p.scale_log2, -base));
         sum0 += p0;
         sum1 += p1;
         sv[i >> 1] = pack_bf16(p0, p1);

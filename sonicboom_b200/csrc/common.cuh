@@ -59,6 +59,11 @@ __device__ __forceinline__ float sb_glu_clamped(float gate, float up, float limi
   return a / (1.0f + expf(-alpha * a)) * (b + 1.0f);
 }
 
+// gelu in its tanh form: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), float32 with the accurate tanhf.
+__device__ __forceinline__ float sb_gelu_tanh(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
 // The rotation of one pair (a at index i, b at i + rot/2): lo = a cos - b sin, hi = a sin + b cos,
 // every product and the sum rounded on its own (no fused multiply-add), so that every kernel
 // that rotates gives the same bits whatever the compiler would contract.

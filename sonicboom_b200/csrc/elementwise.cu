@@ -51,7 +51,7 @@ extern "C" int sb_embed(const int32_t* tokens, int n_rows, const void* table, in
 // order), so a row's result does not depend on which other rows are in the launch.
 // `rows`, when given, gathers: output row r is the norm of input row rows[r].
 template <typename TW, typename TO>
-__global__ void rmsnorm_kernel(const float* x, const int32_t* rows,
+__global__ void rmsnorm_kernel(const float* x, size_t x_ld, const int32_t* rows,
                                const TW* __restrict__ w, int width, float eps,
                                TO* __restrict__ out) {
   __shared__ float warp_sums[32];
@@ -59,7 +59,7 @@ __global__ void rmsnorm_kernel(const float* x, const int32_t* rows,
   sb_pdl_launch();
   sb_pdl_wait();
   const int r = blockIdx.x;
-  const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * x_ld;
   float s = 0.0f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     const float v = xr[i];
@@ -116,13 +116,13 @@ constexpr int NORM_THREADS = 256, NORM_VEC = 4;      // 256 threads x 4 vectors 
 
 template <typename TW, typename TO>
 __global__ void __launch_bounds__(NORM_THREADS)
-rmsnorm_vec_kernel(const float* x, const int32_t* rows, const TW* __restrict__ w, int width,
+rmsnorm_vec_kernel(const float* x, size_t x_ld, const int32_t* rows, const TW* __restrict__ w, int width,
                    float eps, TO* __restrict__ out) {
   __shared__ float warp_sums[NORM_THREADS / 32];
   __shared__ float inv_shared;
   sb_pdl_launch();
   const int r = blockIdx.x;
-  const float* xr = x + (size_t)(rows ? rows[r] : r) * width;     // `rows` is part of the step's plan
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * x_ld;      // `rows` is part of the step's plan
   sb_pdl_wait();
   float v[NORM_VEC][4];
   float s = 0.0f;
@@ -163,20 +163,29 @@ rmsnorm_vec_kernel(const float* x, const int32_t* rows, const TW* __restrict__ w
 extern "C" int sb_rmsnorm(const float* x, const int32_t* rows, int n_rows, int width,
                           const void* weight, int weight_dtype, float eps, void* out,
                           int out_dtype, cudaStream_t stream) {
-  if (n_rows <= 0 || width <= 0) SB_FAIL(SB_ERR_ARG, "sb_rmsnorm: n_rows=%d width=%d", n_rows, width);
+  return sb_rmsnorm_ld(x, width, rows, n_rows, width, weight, weight_dtype, eps, out, out_dtype, stream);
+}
+
+// The same over the first `width` values of input rows that lie `x_ld` values apart.
+extern "C" int sb_rmsnorm_ld(const float* x, int x_ld, const int32_t* rows, int n_rows, int width,
+                             const void* weight, int weight_dtype, float eps, void* out,
+                             int out_dtype, cudaStream_t stream) {
+  if (n_rows <= 0 || width <= 0 || x_ld < width)
+    SB_FAIL(SB_ERR_ARG, "sb_rmsnorm: n_rows=%d width=%d rows %d apart", n_rows, width, x_ld);
   if (!sb_valid_dtype(weight_dtype) || !sb_valid_dtype(out_dtype))
     SB_FAIL(SB_ERR_ARG, "sb_rmsnorm: dtype codes %d %d", weight_dtype, out_dtype);
   if (!(eps >= 0.0f)) SB_FAIL(SB_ERR_ARG, "sb_rmsnorm: eps %g", eps);
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-  const bool vec = width % 4 == 0 && width <= NORM_THREADS * NORM_VEC * 4 &&
+  const bool vec = width % 4 == 0 && x_ld % 4 == 0 && width <= NORM_THREADS * NORM_VEC * 4 &&
                    (((uintptr_t)x | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
   SB_DISPATCH_DTYPE(weight_dtype, TW, {
     SB_DISPATCH_DTYPE(out_dtype, TO, {
       if (vec)
-        sb_launch<SB_K_ELEMENTWISE>(rmsnorm_vec_kernel<TW, TO>, dim3(n_rows), dim3(NORM_THREADS), 0, stream, x, rows,
+        sb_launch<SB_K_ELEMENTWISE>(rmsnorm_vec_kernel<TW, TO>, dim3(n_rows), dim3(NORM_THREADS), 0, stream, x,
+                  (size_t)x_ld, rows,
                   (const TW*)weight, width, eps, (TO*)out);
       else
-        sb_launch<SB_K_ELEMENTWISE>(rmsnorm_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, x, rows,
+        sb_launch<SB_K_ELEMENTWISE>(rmsnorm_kernel<TW, TO>, dim3(n_rows), dim3(threads), 0, stream, x, (size_t)x_ld, rows,
                   (const TW*)weight, width, eps, (TO*)out);
     });
   });

@@ -13,8 +13,9 @@
 //                    cache write, and the rotated query parts into the wide query rows;
 //   sb_head_linear:  out[r, h, :] = W[h] in[r, h, :], a small product per head over strided rows.
 //
-// Rotation: interleaved pairs.  Of a rotated vector, elements 2i and 2i + 1 (i < rot / 2) turn by
-// the angle float(pos) * inv_freq[i]; elements from `rot` on pass unchanged.
+// Rotation: of a rotated vector, elements 2i and 2i + 1 (interleaved pairs) or i and i + rot/2
+// (i < rot / 2) turn by the angle float(pos) * inv_freq[i], cosine and sine times `rot_scale`;
+// elements from `rot` on pass unchanged.
 #include "common.cuh"
 
 namespace {
@@ -27,7 +28,8 @@ __global__ void __launch_bounds__(PREP_THREADS)
 latent_prep_kernel(const float* proj, int ld, int n_heads, int dim, int rd, int rank, int rot,
                    const float* __restrict__ inv_freq, const int32_t* row_seq, const int32_t* row_pos,
                    const int32_t* page_off, const int32_t* page_ids, int page_size,
-                   const TW* __restrict__ cnorm, float eps, TC* cache, TQ* q_wide, int q_group, int has_kv) {
+                   const TW* __restrict__ cnorm, float eps, TC* cache, TQ* q_wide, int q_group, int has_kv,
+                   const float* kv, int kv_ld, int interleaved, float rot_scale) {
   __shared__ float cs[MAX_ROT_PAIRS], sn[MAX_ROT_PAIRS];
   __shared__ float red[PREP_THREADS / 32 + 1];
   sb_pdl_launch();
@@ -36,9 +38,19 @@ latent_prep_kernel(const float* proj, int ld, int n_heads, int dim, int rd, int 
   const int half = rot >> 1;
   for (int i = tid; i < half; i += PREP_THREADS) {
     const float theta = (float)pos * inv_freq[i];
-    cs[i] = cosf(theta);
-    sn[i] = sinf(theta);
+    cs[i] = cosf(theta) * rot_scale;
+    sn[i] = sinf(theta) * rot_scale;
   }
+  // element d of a rotated vector v: pairs (2i, 2i + 1), or (i, i + rot/2) when not interleaved
+  auto turned = [&](const float* v, int d) {
+    if (d >= rot) return v[d];
+    if (interleaved) {
+      const int i = d >> 1;
+      return (d & 1) ? sb_rot_hi(v[d - 1], v[d], cs[i], sn[i]) : sb_rot_lo(v[d], v[d + 1], cs[i], sn[i]);
+    }
+    return d < half ? sb_rot_lo(v[d], v[d + half], cs[d], sn[d])
+                    : sb_rot_hi(v[d - half], v[d], cs[d - half], sn[d - half]);
+  };
   int page = -1;
   if (has_kv) {
     const int seq = row_seq[t];
@@ -54,16 +66,13 @@ latent_prep_kernel(const float* proj, int ld, int n_heads, int dim, int rd, int 
   for (int e = tid; e < n_heads * rd; e += PREP_THREADS) {
     const int h = e / rd, d = e % rd;
     const float* qr = src + (size_t)h * hw + dim;
-    float v = qr[d];
-    if (d < rot) {
-      const int i = d >> 1;
-      v = (d & 1) ? sb_rot_hi(qr[d - 1], qr[d], cs[i], sn[i]) : sb_rot_lo(qr[d], qr[d + 1], cs[i], sn[i]);
-    }
+    const float v = turned(qr, d);
     // wide query rows lie [head group][row][head in group]: one group is [row][head]
     q_wide[(((size_t)(h / q_group) * gridDim.x + t) * q_group + h % q_group) * wide + rank + d] = sb_from_f32<TQ>(v);
   }
   if (!has_kv) return;
-  const float* lat = src + (size_t)n_heads * hw;
+  // the latent and the shared key part: after the heads in the same row, or rows of their own
+  const float* lat = kv ? kv + (size_t)t * kv_ld : src + (size_t)n_heads * hw;
   float s = 0.0f;
   for (int i = tid; i < rank; i += PREP_THREADS) s = fmaf(lat[i], lat[i], s);
   s = sb_warp_sum(s);
@@ -86,12 +95,7 @@ latent_prep_kernel(const float* proj, int ld, int n_heads, int dim, int rd, int 
   }
   const float* kr = lat + rank;
   for (int d = tid; d < rd; d += PREP_THREADS) {
-    float v = kr[d];
-    if (d < rot) {
-      const int i = d >> 1;
-      v = (d & 1) ? sb_rot_hi(kr[d - 1], kr[d], cs[i], sn[i]) : sb_rot_lo(kr[d], kr[d + 1], cs[i], sn[i]);
-    }
-    krow[rank + d] = sb_from_f32<TC>(v);
+    krow[rank + d] = sb_from_f32<TC>(turned(kr, d));
     vrow[rank + d] = sb_from_f32<TC>(0.0f);
   }
 }
@@ -252,7 +256,9 @@ extern "C" int sb_latent_prep(const float* proj, int n_rows, int n_heads, int di
                               const int32_t* row_pos, const int32_t* page_off, const int32_t* page_ids,
                               int page_size, const void* cnorm, int cnorm_dtype, float eps, void* cache,
                               int cache_dtype, void* q_wide, int q_dtype, int q_group, int has_kv,
-                              cudaStream_t stream) {
+                              const float* kv, int kv_ld, int interleaved, float rot_scale, cudaStream_t stream) {
+  if (kv && (!has_kv || kv_ld < rank + rd))
+    SB_FAIL(SB_ERR_ARG, "sb_latent_prep: latent rows of their own need a cache write and %d values a row", rank + rd);
   if (q_group <= 0 || n_heads % q_group)
     SB_FAIL(SB_ERR_ARG, "sb_latent_prep: groups of %d heads do not divide %d heads", q_group, n_heads);
   if (n_rows <= 0 || n_heads <= 0 || dim < 0 || rd < 0 || rank <= 0 || !proj || !q_wide || !row_pos)
@@ -264,13 +270,14 @@ extern "C" int sb_latent_prep(const float* proj, int n_rows, int n_heads, int di
     SB_FAIL(SB_ERR_ARG, "sb_latent_prep: a cache write needs the cache, its norm weight and the page tables");
   if (!sb_valid_dtype(q_dtype) || (has_kv && (!sb_valid_dtype(cache_dtype) || !sb_valid_dtype(cnorm_dtype))))
     SB_FAIL(SB_ERR_ARG, "sb_latent_prep: dtype codes %d %d %d", q_dtype, cache_dtype, cnorm_dtype);
-  const int ld = n_heads * (dim + rd) + (has_kv ? rank + rd : 0);
+  const int ld = n_heads * (dim + rd) + (has_kv && !kv ? rank + rd : 0);
   SB_DISPATCH_DTYPE(has_kv ? cnorm_dtype : SB_F32, TW, {
     SB_DISPATCH_DTYPE(has_kv ? cache_dtype : SB_F32, TC, {
       SB_DISPATCH_DTYPE(q_dtype, TQ, {
         sb_launch<SB_K_ELEMENTWISE>(latent_prep_kernel<TW, TC, TQ>, dim3(n_rows), dim3(PREP_THREADS), 0, stream,
                                     proj, ld, n_heads, dim, rd, rank, rot, inv_freq, row_seq, row_pos, page_off,
-                                    page_ids, page_size, (const TW*)cnorm, eps, (TC*)cache, (TQ*)q_wide, q_group, has_kv);
+                                    page_ids, page_size, (const TW*)cnorm, eps, (TC*)cache, (TQ*)q_wide, q_group, has_kv,
+                                    kv, kv_ld, interleaved, rot_scale);
       });
     });
   });

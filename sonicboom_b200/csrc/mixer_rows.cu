@@ -118,8 +118,12 @@ struct PrepArgs {
   int rot, interleaved;
   const float* inv_freq;               // [rot / 2]
   const float* v_inv_freq;             // [vdim / 2], or null: values are not rotated
-  const void* q_norm;                  // [n_q_heads * dim] or null
-  const void* k_norm;                  // [n_kv_heads * dim] or null
+  const void* q_norm;                  // [n_q_heads * dim] or null ([dim] with head_norm 1)
+  const void* k_norm;                  // [n_kv_heads * dim] or null ([dim] with head_norm 1)
+  int head_norm;                       // 0: the norm, if any, is over the whole projection; 1: every head by itself
+                                       // before the rotation, one weight [dim] for all heads; 2: every head by
+                                       // itself after the rotation, no weight
+  float rot_scale;                     // multiplies every cosine and sine (1: a pure rotation)
   float eps;
   const int32_t* row_seq;
   const int32_t* row_pos;
@@ -136,7 +140,8 @@ struct PrepArgs {
 // to one pair and walks over the heads, so the pair's sine and cosine are worked out once.
 template <int NT, typename Get, typename Put>
 __device__ __forceinline__ void turn_heads(int heads, int n_in, int n_out, int rot, int interleaved,
-                                           const float* __restrict__ inv_freq, float fpos, Get get, Put put) {
+                                           const float* __restrict__ inv_freq, float fpos, Get get, Put put,
+                                           float rot_scale = 1.0f) {
   const int n_pairs = rot >> 1;
   if (n_pairs > 0) {
     const int groups = NT / n_pairs > 0 ? NT / n_pairs : 1;      // thread groups that take heads in turn
@@ -145,6 +150,8 @@ __device__ __forceinline__ void turn_heads(int heads, int n_in, int n_out, int r
       if (first_head < groups) {
         float sn, cs;
         sincosf(fpos * inv_freq[i], &sn, &cs);
+        sn *= rot_scale;
+        cs *= rot_scale;
         const int lo = interleaved ? 2 * i : i, hi = interleaved ? 2 * i + 1 : i + n_pairs;
         for (int h = first_head; h < heads; h += groups) {
           const float a = get(h, lo), b = get(h, hi);
@@ -156,6 +163,8 @@ __device__ __forceinline__ void turn_heads(int heads, int n_in, int n_out, int r
       for (int j = threadIdx.x; j < n_pairs; j += NT) {          // more pairs than threads
         float sn, cs;
         sincosf(fpos * inv_freq[j], &sn, &cs);
+        sn *= rot_scale;
+        cs *= rot_scale;
         const int lo = interleaved ? 2 * j : j, hi = interleaved ? 2 * j + 1 : j + n_pairs;
         for (int h = 0; h < heads; ++h) {
           const float a = get(h, lo), b = get(h, hi);
@@ -203,6 +212,58 @@ __global__ void __launch_bounds__(NT) attn_prep_kernel(const PrepArgs p) {
   const float* src = row + (what == 0 ? p.q_off : p.k_off);
   const TW* nw = reinterpret_cast<const TW*>(what == 0 ? p.q_norm : p.k_norm);
   const int dim = p.dim;
+  if (p.head_norm) {
+    // Every head is normed by itself: before the rotation with one weight for all heads (1), or
+    // after it without a weight (2).  The turned heads wait in shared memory ([heads, dim], then
+    // one inverse root mean square per head) until the head's sum is known; a warp sums a head.
+    extern __shared__ float staged[];
+    float* hinv = staged + heads * dim;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (p.head_norm == 1) {
+      for (int h = warp; h < heads; h += NT / 32) {
+        float s = 0.0f;
+        for (int c = lane; c < dim; c += 32) s = fmaf(src[h * dim + c], src[h * dim + c], s);
+        s = sb_warp_sum(s);
+        if (lane == 0) hinv[h] = 1.0f / sqrtf(s / (float)dim + p.eps);
+      }
+      __syncthreads();
+    }
+    const bool pre = p.head_norm == 1;
+    turn_heads<NT>(heads, dim, dim, p.rot, p.interleaved, p.inv_freq, fpos,
+                   [&](int h, int c) {
+                     const float v = src[h * dim + c];
+                     return pre ? (v * hinv[h]) * sb_to_f32<TW>(nw[c]) : v;
+                   },
+                   [&](int h, int c, float v) { staged[h * dim + c] = v; }, p.rot_scale);
+    __syncthreads();
+    if (!pre) {
+      for (int h = warp; h < heads; h += NT / 32) {
+        float s = 0.0f;
+        for (int c = lane; c < dim; c += 32) s = fmaf(staged[h * dim + c], staged[h * dim + c], s);
+        s = sb_warp_sum(s);
+        if (lane == 0) hinv[h] = 1.0f / sqrtf(s / (float)dim + p.eps);
+      }
+      __syncthreads();
+    }
+    const int hd = p.hd;
+    if (what == 0) {
+      TQ* dst = reinterpret_cast<TQ*>(p.q_out) + (size_t)t * p.n_q_heads * hd;
+      for (int e = threadIdx.x; e < heads * hd; e += NT) {
+        const int h = e / hd, c = e % hd;
+        dst[e] = sb_from_f32<TQ>(c < dim ? (pre ? staged[h * dim + c] : staged[h * dim + c] * hinv[h]) : 0.0f);
+      }
+    } else {
+      TC* dst = reinterpret_cast<TC*>(p.cache) +
+                ((((size_t)page * 2) * p.n_kv_heads) * p.page_size + pos % p.page_size) * hd;
+      const size_t head_step = (size_t)p.page_size * hd;
+      for (int e = threadIdx.x; e < heads * hd; e += NT) {
+        const int h = e / hd, c = e % hd;
+        dst[h * head_step + c] =
+            sb_from_f32<TC>(c < dim ? (pre ? staged[h * dim + c] : staged[h * dim + c] * hinv[h]) : 0.0f);
+      }
+    }
+    return;
+  }
   float inv = 1.0f;
   if (nw) {
     float s = 0.0f;
@@ -217,13 +278,13 @@ __global__ void __launch_bounds__(NT) attn_prep_kernel(const PrepArgs p) {
     TQ* dst = reinterpret_cast<TQ*>(p.q_out) + (size_t)t * p.n_q_heads * p.hd;
     const int hd = p.hd;
     turn_heads<NT>(heads, dim, hd, p.rot, p.interleaved, p.inv_freq, fpos, get,
-                   [&](int h, int c, float v) { dst[h * hd + c] = sb_from_f32<TQ>(v); });
+                   [&](int h, int c, float v) { dst[h * hd + c] = sb_from_f32<TQ>(v); }, p.rot_scale);
   } else {
     TC* dst = reinterpret_cast<TC*>(p.cache) +
               ((((size_t)page * 2) * p.n_kv_heads) * p.page_size + pos % p.page_size) * p.hd;
     const size_t head_step = (size_t)p.page_size * p.hd;
     turn_heads<NT>(heads, dim, p.hd, p.rot, p.interleaved, p.inv_freq, fpos, get,
-                   [&](int h, int c, float v) { dst[h * head_step + c] = sb_from_f32<TC>(v); });
+                   [&](int h, int c, float v) { dst[h * head_step + c] = sb_from_f32<TC>(v); }, p.rot_scale);
   }
 }
 
@@ -231,7 +292,7 @@ __global__ void __launch_bounds__(NT) attn_prep_kernel(const PrepArgs p) {
 template <int NT, typename T>
 __global__ void __launch_bounds__(NT)
 attn_unrotate_kernel(const T* in, T* out, int n_heads, int hd, int vdim, int interleaved,
-                     const float* __restrict__ v_inv_freq, const int32_t* row_pos) {
+                     const float* __restrict__ v_inv_freq, const int32_t* row_pos, const float* gate, int gate_ld) {
   sb_pdl_launch();
   const size_t t = blockIdx.x;
   const float fpos = v_inv_freq ? -(float)row_pos[t] : 0.0f;
@@ -241,7 +302,7 @@ attn_unrotate_kernel(const T* in, T* out, int n_heads, int hd, int vdim, int int
   if constexpr (sizeof(T) == 2) {
     // neighbouring pairs of 16-bit values: a pair is one 4-byte access
     const int n_pairs = vdim >> 1;
-    if (v_inv_freq && interleaved && !(hd & 1) && !(vdim & 1) && n_pairs <= NT) {
+    if (v_inv_freq && !gate && interleaved && !(hd & 1) && !(vdim & 1) && n_pairs <= NT) {
       const int groups = NT / n_pairs, i = threadIdx.x % n_pairs, first_head = threadIdx.x / n_pairs;
       if (first_head >= groups) return;
       float sn, cs;
@@ -257,7 +318,11 @@ attn_unrotate_kernel(const T* in, T* out, int n_heads, int hd, int vdim, int int
   }
   turn_heads<NT>(n_heads, vdim, vdim, v_inv_freq ? vdim : 0, interleaved, v_inv_freq, fpos,
                  [&](int h, int c) { return sb_to_f32<T>(src[h * hd + c]); },
-                 [&](int h, int c, float v) { dst[h * vdim + c] = sb_from_f32<T>(v); });
+                 [&](int h, int c, float v) {
+                   // a gate: the head's result times the logistic function of the row's number for that head
+                   if (gate) v = v / (1.0f + expf(-gate[t * gate_ld + h]));
+                   dst[h * vdim + c] = sb_from_f32<T>(v);
+                 });
 }
 
 // ---------------------------------------------------------------------- linear recurrence
@@ -387,10 +452,10 @@ extern "C" int sb_polynorm(const float* z, int n_rows, int ff, const void* coef,
 extern "C" int sb_attn_prep(const float* proj, int n_rows, int ld, int q_off, int k_off, int v_off,
                             int n_q_heads, int n_kv_heads, int dim, int vdim, int hd, int rot, int interleaved,
                             const float* inv_freq, const float* v_inv_freq, const void* q_norm,
-                            const void* k_norm, int norm_dtype, float eps, const int32_t* row_seq,
-                            const int32_t* row_pos, const int32_t* page_off, const int32_t* page_ids,
-                            int page_size, void* cache, int cache_dtype, void* q_out, int q_dtype, int has_kv,
-                            cudaStream_t stream) {
+                            const void* k_norm, int norm_dtype, int head_norm, float rot_scale, float eps,
+                            const int32_t* row_seq, const int32_t* row_pos, const int32_t* page_off,
+                            const int32_t* page_ids, int page_size, void* cache, int cache_dtype, void* q_out,
+                            int q_dtype, int has_kv, cudaStream_t stream) {
   if (n_rows <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 || dim <= 0 || vdim <= 0 || hd < dim || hd < vdim)
     SB_FAIL(SB_ERR_ARG, "sb_attn_prep: rows=%d heads=%d/%d dim=%d vdim=%d hd=%d", n_rows, n_q_heads, n_kv_heads,
             dim, vdim, hd);
@@ -403,7 +468,15 @@ extern "C" int sb_attn_prep(const float* proj, int n_rows, int ld, int q_off, in
   if (!proj || !q_out || !row_pos || (has_kv && (!cache || !row_seq || !page_off || !page_ids || page_size <= 0)))
     SB_FAIL(SB_ERR_ARG, "sb_attn_prep: arguments missing");
   if ((q_norm == nullptr) != (k_norm == nullptr)) SB_FAIL(SB_ERR_ARG, "sb_attn_prep: one of the two norms is missing");
+  if (head_norm < 0 || head_norm > 2 || (head_norm == 1 && !q_norm) || (head_norm == 2 && q_norm))
+    SB_FAIL(SB_ERR_ARG, "sb_attn_prep: head_norm %d (1 needs the two weights, 2 takes none)", head_norm);
+  const int most_heads = n_q_heads > n_kv_heads ? n_q_heads : n_kv_heads;
+  const size_t staged = head_norm ? ((size_t)most_heads * dim + most_heads) * sizeof(float) : 0;
+  if (staged > 200 * 1024)
+    SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attn_prep: %d heads of %d values do not fit shared memory for per-head norms",
+            most_heads, dim);
   PrepArgs p;
+  p.head_norm = head_norm; p.rot_scale = rot_scale;
   p.proj = proj; p.ld = ld; p.q_off = q_off; p.k_off = k_off; p.v_off = v_off;
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.dim = dim; p.vdim = vdim; p.hd = hd;
   p.rot = rot; p.interleaved = interleaved; p.inv_freq = inv_freq; p.v_inv_freq = v_inv_freq;
@@ -415,7 +488,11 @@ extern "C" int sb_attn_prep(const float* proj, int n_rows, int ld, int q_off, in
   SB_DISPATCH_DTYPE(q_norm ? norm_dtype : SB_F32, TW, {
     SB_DISPATCH_DTYPE(q_dtype, TQ, {
       SB_DISPATCH_DTYPE(has_kv ? cache_dtype : SB_F32, TC, {
-        sb_launch<SB_K_ELEMENTWISE>(attn_prep_kernel<NT, TW, TQ, TC>, grid, dim3(NT), 0, stream, p);
+        if (staged > 48 * 1024 &&
+            cudaFuncSetAttribute(attn_prep_kernel<NT, TW, TQ, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)staged) != cudaSuccess)
+          SB_FAIL(SB_ERR_CUDA, "sb_attn_prep: shared memory opt-in failed");
+        sb_launch<SB_K_ELEMENTWISE>(attn_prep_kernel<NT, TW, TQ, TC>, grid, dim3(NT), staged, stream, p);
       });
     });
   });
@@ -425,13 +502,13 @@ extern "C" int sb_attn_prep(const float* proj, int n_rows, int ld, int q_off, in
 
 extern "C" int sb_attn_unrotate(const void* in, void* out, int dtype, int n_rows, int n_heads, int hd, int vdim,
                                 int interleaved, const float* v_inv_freq, const int32_t* row_pos,
-                                cudaStream_t stream) {
+                                const float* gate, int gate_ld, cudaStream_t stream) {
   if (n_rows <= 0 || n_heads <= 0 || vdim <= 0 || hd < vdim || !in || !out || !sb_valid_dtype(dtype))
     SB_FAIL(SB_ERR_ARG, "sb_attn_unrotate: rows=%d heads=%d hd=%d vdim=%d dtype=%d", n_rows, n_heads, hd, vdim, dtype);
   if (v_inv_freq && (vdim % 2 || !row_pos)) SB_FAIL(SB_ERR_ARG, "sb_attn_unrotate: rotation needs an even vdim and positions");
   SB_DISPATCH_DTYPE(dtype, T, {
     sb_launch<SB_K_ELEMENTWISE>(attn_unrotate_kernel<256, T>, dim3(n_rows), dim3(256), 0, stream, (const T*)in, (T*)out,
-                                n_heads, hd, vdim, interleaved, v_inv_freq, row_pos);
+                                n_heads, hd, vdim, interleaved, v_inv_freq, row_pos, gate, gate_ld);
   });
   SB_CHECK_LAUNCH("sb_attn_unrotate");
   return SB_OK;

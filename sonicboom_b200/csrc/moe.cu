@@ -98,6 +98,113 @@ moe_route_warp_kernel(const float* logits, int n_rows, int n_experts, int top, i
   }
 }
 
+// The choice with scores that are logistic functions of the logits (a warp per row, up to 1024
+// experts).  s_e = sigmoid(z_e); the choice score is s_e + correction_e.  The experts lie in
+// `n_groups` equal groups of neighbours; a group's score is the sum of its `group_top` largest
+// choice scores, and only experts of the `keep_groups` best groups can be chosen (n_groups 1:
+// every expert can).  The `top` experts with the largest choice scores are chosen (the lower
+// index wins a tie); their weights are s_e * scale, divided by the chosen ones' sum of s when
+// `renormalize`.  All float32.  `sc` holds a warp's choice scores (minus infinity once an expert
+// is chosen or its group is out), `gs` its group scores.
+constexpr int ROUTE_WARPS = 4, ROUTE_MAX_EXPERTS = 1024;
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_scored_kernel(const float* logits, const float* __restrict__ correction, int n_rows, int n_experts,
+                        int top, int n_groups, int keep_groups, int group_top, float scale, int renormalize,
+                        int32_t* ids, float* weights) {
+  __shared__ float sc_all[ROUTE_WARPS][ROUTE_MAX_EXPERTS];
+  __shared__ float gs_all[ROUTE_WARPS][ROUTE_MAX_EXPERTS];
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = blockIdx.x * ROUTE_WARPS + warp;
+  if (r >= n_rows) return;
+  float* sc = sc_all[warp];
+  float* gs = gs_all[warp];
+  const float* z = logits + (size_t)r * n_experts;
+  for (int e = lane; e < n_experts; e += 32) {
+    const float s = 1.0f / (1.0f + expf(-z[e]));
+    sc[e] = s + (correction ? correction[e] : 0.0f);
+  }
+  __syncwarp();
+  if (n_groups > 1) {
+    const int per = n_experts / n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+      // the sum of the group's `group_top` largest choice scores, largest first
+      float sum = 0.0f, bound = INFINITY;
+      int bound_at = -1;
+      for (int k = 0; k < group_top && k < per; ++k) {
+        float bv = -INFINITY;
+        int best = -1;
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+          const float v = sc[e];
+          const bool below = v < bound || (v == bound && e > bound_at);     // not taken yet
+          if (below && (best < 0 || v > bv)) best = e, bv = v;
+        }
+        sum += bv;
+        bound = bv;
+        bound_at = best;
+      }
+      gs[g] = sum;
+    }
+    __syncwarp();
+    // the best groups keep their score's sign bit out of the way: mark the kept ones, then close the rest
+    for (int k = 0; k < keep_groups; ++k) {
+      int best = INT_MAX;
+      float bv = -INFINITY;
+      for (int g = lane; g < n_groups; g += 32) {
+        const float v = gs[g];
+        if (v != INFINITY && (best == INT_MAX || v > bv)) best = g, bv = v;
+      }
+#pragma unroll
+      for (int off = 16; off; off >>= 1) {
+        const int og = __shfl_xor_sync(0xffffffffu, best, off);
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+        if (og != INT_MAX && (best == INT_MAX || ov > bv || (ov == bv && og < best))) best = og, bv = ov;
+      }
+      if (lane == 0 && best != INT_MAX) gs[best] = INFINITY;              // kept
+      __syncwarp();
+    }
+    for (int e = lane; e < n_experts; e += 32)
+      if (gs[e / per] != INFINITY) sc[e] = -INFINITY;
+    __syncwarp();
+  }
+  int32_t* id = ids + (size_t)r * top;
+  float* w = weights + (size_t)r * top;
+  float total = 0.0f;
+  for (int k = 0; k < top; ++k) {
+    int best = INT_MAX;
+    float bv = -INFINITY;
+    for (int e = lane; e < n_experts; e += 32) {
+      const float v = sc[e];
+      if (v != -INFINITY && (best == INT_MAX || v > bv)) best = e, bv = v;
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) {
+      const int oe = __shfl_xor_sync(0xffffffffu, best, off);
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      if (oe != INT_MAX && (best == INT_MAX || ov > bv || (ov == bv && oe < best))) best = oe, bv = ov;
+    }
+    // fewer experts in the kept groups than `top`: the rest of the choices repeat nothing, they
+    // point at expert 0 with weight 0
+    if (lane == 0) {
+      if (best == INT_MAX) {
+        id[k] = 0;
+        w[k] = 0.0f;
+      } else {
+        const float s = 1.0f / (1.0f + expf(-z[best]));
+        id[k] = best;
+        w[k] = s;
+        total += s;
+        sc[best] = -INFINITY;
+      }
+    }
+    __syncwarp();
+  }
+  if (lane == 0)
+    for (int k = 0; k < top; ++k) w[k] = renormalize ? w[k] / total * scale : w[k] * scale;
+}
+
 // meta: [0] number of tiles; then per tile (expert, first place in `order`, pairs).
 __global__ void __launch_bounds__(1024)
 moe_group_kernel(const int32_t* ids, int n_pairs, int n_experts, int tile_rows, int32_t* order, int32_t* meta) {
@@ -411,6 +518,26 @@ extern "C" int sb_moe_route(const float* logits, int n_rows, int n_experts, int 
     sb_launch<SB_K_ELEMENTWISE>(moe_route_kernel, dim3((n_rows + 127) / 128), dim3(128), 0, stream, logits, n_rows,
                                 n_experts, top, ids, weights);
   SB_CHECK_LAUNCH("sb_moe_route");
+  return SB_OK;
+}
+
+extern "C" int sb_moe_route_scored(const float* logits, const float* correction, int n_rows, int n_experts, int top,
+                                   int n_groups, int keep_groups, int group_top, float scale, int renormalize,
+                                   int32_t* ids, float* weights, cudaStream_t stream) {
+  if (n_rows <= 0 || n_experts <= 0 || top <= 0 || top > n_experts || !logits || !ids || !weights)
+    SB_FAIL(SB_ERR_ARG, "sb_moe_route_scored: rows=%d experts=%d top=%d", n_rows, n_experts, top);
+  if (n_experts > ROUTE_MAX_EXPERTS)
+    SB_FAIL(SB_ERR_UNSUPPORTED, "sb_moe_route_scored: %d experts (at most %d)", n_experts, ROUTE_MAX_EXPERTS);
+  if (n_groups < 1 || n_experts % n_groups || keep_groups < 1 || keep_groups > n_groups || group_top < 1)
+    SB_FAIL(SB_ERR_ARG, "sb_moe_route_scored: %d groups of %d experts, %d kept, %d scores a group", n_groups, n_experts,
+            keep_groups, group_top);
+  if ((long long)keep_groups * (n_experts / n_groups) < top)
+    SB_FAIL(SB_ERR_ARG, "sb_moe_route_scored: %d kept groups of %d experts cannot give %d choices", keep_groups,
+            n_experts / n_groups, top);
+  sb_launch<SB_K_ELEMENTWISE>(moe_route_scored_kernel, dim3((n_rows + ROUTE_WARPS - 1) / ROUTE_WARPS),
+                              dim3(ROUTE_WARPS * 32), 0, stream, logits, correction, n_rows, n_experts, top, n_groups,
+                              keep_groups, group_top, scale, renormalize, ids, weights);
+  SB_CHECK_LAUNCH("sb_moe_route_scored");
   return SB_OK;
 }
 

@@ -36,6 +36,8 @@ enum SbStatus { SB_OK = 0, SB_ERR_ARG = 1, SB_ERR_UNSUPPORTED = 2, SB_ERR_CUDA =
  * blocks of 8 (8 gate rows, the 8 up rows of the same outputs); out[m, o] = silu(gate) * up and
  * has N / 2 columns. */
 enum SbEpilogue { SB_EPI_NONE = 0, SB_EPI_BIAS = 1, SB_EPI_RESIDUAL = 2, SB_EPI_SWIGLU = 3 };
+/* The activation of a gated feed-forward: act(gate) * up. */
+enum SbGate { SB_GATE_SILU = 0, SB_GATE_CLAMPED = 1, SB_GATE_GELU_TANH = 2 };
 /* Kernel classes: bits of the mask that says which kernels are launched with programmatic
  * dependent launch (sb_set_pdl). */
 enum SbKernelClass {
@@ -100,6 +102,9 @@ int sb_embed(const int32_t* tokens, int n_rows, const void* table, int table_dty
 /* out[r] = x[rows ? rows[r] : r] / sqrt(mean(x^2) + eps) * weight */
 int sb_rmsnorm(const float* x, const int32_t* rows, int n_rows, int width, const void* weight,
                int weight_dtype, float eps, void* out, int out_dtype, sb_stream_t stream);
+/* The same over the first `width` values of input rows that lie x_ld values apart. */
+int sb_rmsnorm_ld(const float* x, int x_ld, const int32_t* rows, int n_rows, int width, const void* weight,
+                  int weight_dtype, float eps, void* out, int out_dtype, sb_stream_t stream);
 int sb_softcap(float* x, size_t n, float cap, sb_stream_t stream);     /* x = cap tanh(x / cap) */
 int sb_add_bias(float* x, const void* bias, int bias_dtype, int rows, int width, sb_stream_t stream);   /* x[m, n] += bias[n] */
 int sb_cast(const void* in, int in_dtype, void* out, int out_dtype, size_t n, sb_stream_t stream);
@@ -165,6 +170,11 @@ int sb_depth_mix(float* planes, size_t plane, int n_inputs, const void* coef, in
  * b = clamp(up, -limit, limit). */
 int sb_glu_clamped(const float* gu, int n_rows, int ff, float limit, float alpha, int interleaved,
                    void* out, int out_dtype, sb_stream_t stream);
+/* The same rows with the activation named by `kind` (SbGate): silu(gate) * up, the clamped form of
+ * sb_glu_clamped, or gelu(gate) * up with gelu(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))). */
+int sb_gated_act(const float* gu, int n_rows, int ff, int kind, float limit, float alpha, int interleaved,
+                 void* out, int out_dtype, sb_stream_t stream);
+int sb_scale(float* x, size_t n, float c, sb_stream_t stream);          /* x *= c */
 
 /* ---- attention over a cached latent ----
  * proj[r] = [n_heads x (dim | rd) | rank | rd] (the last two only with has_kv).  Rotates the first
@@ -172,12 +182,15 @@ int sb_glu_clamped(const float* gu, int n_rows, int ff, float limit, float alpha
  * writes each head's rotated part to q_wide[r, h, rank : rank + rd] (q_wide lies [head group][row][head
  * in group][rank + rd] with groups of q_group heads; q_group = n_heads is [row][head]); with has_kv, RMS-norms the
  * latent (weight cnorm, eps) and writes the page row of the position: key plane [latent | rotated
- * key part], value plane [latent | zeros].  The cache entry has one head of size rank + rd. */
+ * key part], value plane [latent | zeros].  The cache entry has one head of size rank + rd.
+ * `kv` (or null): rows [rank | rd] of their own, kv_ld values apart, instead of the tail of proj's rows.
+ * interleaved = 0: the pairs are (i, i + rot/2).  rot_scale multiplies every cosine and sine. */
 int sb_latent_prep(const float* proj, int n_rows, int n_heads, int dim, int rd, int rank, int rot,
                    const float* inv_freq, const int32_t* row_seq, const int32_t* row_pos,
                    const int32_t* page_off, const int32_t* page_ids, int page_size, const void* cnorm,
                    int cnorm_dtype, float eps, void* cache, int cache_dtype, void* q_wide, int q_dtype,
-                   int q_group, int has_kv, sb_stream_t stream);
+                   int q_group, int has_kv, const float* kv, int kv_ld, int interleaved, float rot_scale,
+                   sb_stream_t stream);
 /* out[r * out_ld + h * out_hs + n] = sum_k in[r * in_ld + h * in_hs + k] * W[(h * N + n) * K + k] */
 int sb_head_linear(const void* in, int in_dtype, size_t in_ld, size_t in_hs, const void* W, int w_dtype,
                    int n_rows, int n_heads, int N, int K, void* out, int out_dtype, size_t out_ld,
@@ -204,7 +217,7 @@ int sb_attention_plain(const void* q, void* out, int act_dtype, int n_rows, cons
                        const int32_t* row_pos, const int32_t* page_off, const int32_t* page_ids,
                        int page_size, const void* cache, int cache_dtype, int n_q_heads,
                        int n_kv_heads, int hd, int window, float scale, const float* sink,
-                       sb_stream_t stream);
+                       float softcap, sb_stream_t stream);
 
 /* ---- the stream, the feed-forward and mixers with projections of their own kind ----
  * out[r] = x[r] + add[r] + vec (add [rows, width] float32 and vec [width] are optional; out may be
@@ -223,19 +236,23 @@ int sb_polynorm(const float* z, int n_rows, int ff, const void* coef, int coef_d
  * q_norm / k_norm the whole q (k) projection of a row is RMS-normed with that weight first.  The
  * first `rot` values of every q and k head turn by float(pos) * inv_freq[i], in pairs
  * (i, i + rot/2), or (2i, 2i + 1) with `interleaved`; with v_inv_freq [vdim/2] every value head turns
- * the same way over all vdim.  has_kv = 0: queries only. */
+ * the same way over all vdim.  has_kv = 0: queries only.
+ * head_norm 1: every q and k head is RMS-normed by itself before the rotation, q_norm / k_norm being
+ * one weight [dim] for all heads; head_norm 2: every head is divided by its root mean square after the
+ * rotation (no weights).  rot_scale multiplies every cosine and sine of the q and k rotation. */
 int sb_attn_prep(const float* proj, int n_rows, int ld, int q_off, int k_off, int v_off,
                  int n_q_heads, int n_kv_heads, int dim, int vdim, int hd, int rot, int interleaved,
                  const float* inv_freq, const float* v_inv_freq, const void* q_norm,
-                 const void* k_norm, int norm_dtype, float eps, const int32_t* row_seq,
-                 const int32_t* row_pos, const int32_t* page_off, const int32_t* page_ids,
-                 int page_size, void* cache, int cache_dtype, void* q_out, int q_dtype, int has_kv,
-                 sb_stream_t stream);
+                 const void* k_norm, int norm_dtype, int head_norm, float rot_scale, float eps,
+                 const int32_t* row_seq, const int32_t* row_pos, const int32_t* page_off,
+                 const int32_t* page_ids, int page_size, void* cache, int cache_dtype, void* q_out,
+                 int q_dtype, int has_kv, sb_stream_t stream);
 /* out [rows, n_heads * vdim] = the first vdim values of every head of in [rows, n_heads, hd], turned
- * by -float(pos) * v_inv_freq[i] in the same pairs (v_inv_freq null: copied). */
+ * by -float(pos) * v_inv_freq[i] in the same pairs (v_inv_freq null: copied).  With `gate`, head h of
+ * row r is multiplied by sigmoid(gate[r * gate_ld + h]). */
 int sb_attn_unrotate(const void* in, void* out, int dtype, int n_rows, int n_heads, int hd, int vdim,
                      int interleaved, const float* v_inv_freq, const int32_t* row_pos,
-                     sb_stream_t stream);
+                     const float* gate, int gate_ld, sb_stream_t stream);
 /* In place on projection rows: q (at q_off) and k (at k_off), [n_heads x dim] each, are rotated
  * (the first `rot` of every head, pairs as in sb_attn_prep) and multiplied by q_scale / k_scale; z
  * [rows, n_heads * dim], if given, becomes exp(logsigmoid(z) * inv_tau).  With a2 [n_heads * dim,
@@ -322,6 +339,14 @@ int sb_attention_sigmoid(const void* q, void* out, int act_dtype, int n_rows, co
  * (in grouped order); pair_out [pairs, width] float32 (in pair order). */
 int sb_moe_route(const float* logits, int n_rows, int n_experts, int top, int32_t* ids, float* weights,
                  sb_stream_t stream);
+/* Scores s = sigmoid(logits); choice scores s + correction (float32 [experts], or null); the experts
+ * lie in n_groups equal groups of neighbours, a group's score is the sum of its group_top largest
+ * choice scores, and only experts of the keep_groups best groups can be chosen; the `top` largest
+ * choice scores win (the lower index on a tie); weights s * scale, over the chosen ones' sum of s
+ * first when `renormalize`. */
+int sb_moe_route_scored(const float* logits, const float* correction, int n_rows, int n_experts, int top,
+                        int n_groups, int keep_groups, int group_top, float scale, int renormalize,
+                        int32_t* ids, float* weights, sb_stream_t stream);
 /* Pairs of a tile of one expert (32, 64 or 128) that group, up and down of one step share. */
 int sb_moe_tile_rows(int dtype, int n_pairs, int n_experts, int ff, int width);
 int sb_moe_max_tiles(int n_pairs, int n_experts, int tile_rows);
@@ -360,7 +385,7 @@ int sb_attention(const void* q, void* out, int n_rows, int n_seqs, int max_new,
                  const int32_t* page_ids, int page_size, const void* cache, int n_q_heads,
                  int n_kv_heads, int hd, int window, float scale, void* scratch,
                  size_t scratch_bytes, int* counters, int n_counters, int max_len, int n_pages,
-                 int n_sms, const void* warm, size_t warm_bytes, const float* sink,
+                 int n_sms, const void* warm, size_t warm_bytes, const float* sink, float softcap,
                  sb_stream_t stream);
 
 #ifdef __cplusplus

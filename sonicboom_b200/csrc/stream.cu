@@ -2,6 +2,8 @@
 // it, and for models that feed each layer a weighted sum of everything before it.
 //
 //   sb_norm_add:   out[r] = x[r] + y[r] / sqrt(mean(y[r]^2) + eps) * w
+//   sb_gated_act:  out = act(gate) * up over [gate | up] rows: silu, the clamped form, or the tanh form of gelu
+//   sb_scale:      x *= c
 //   sb_depth_mix:  out[r] = sum_j c[j] * planes[j][r]           (j ascending, float32)
 //
 // Both can also deliver the RMS norm of the row they have just finished (the first norm of
@@ -94,8 +96,12 @@ norm_add_kernel(const float* y, const float* x, int width, const TW* __restrict_
       sq = fmaf(v.v[j], v.v[j], sq);
     }
     st<V>(o + i, v);
+    if (normed && !next_w) {             // no norm named: the finished row as it is, in the other dtype
+#pragma unroll
+      for (int j = 0; j < V; ++j) normed[r * width + i + j] = sb_from_f32<TO>(v.v[j]);
+    }
   }
-  if (normed) write_normed<NT, V, TN, TO>(o, width, sq, next_eps, next_w, normed + r * width, red);
+  if (normed && next_w) write_normed<NT, V, TN, TO>(o, width, sq, next_eps, next_w, normed + r * width, red);
 }
 
 constexpr int MIX_MAX = 256;       // most planes one depth mix adds up
@@ -173,6 +179,29 @@ __global__ void glu_clamped_kernel(const float* gu, size_t n, int ff, float limi
   }
 }
 
+// The same row layouts with the activation chosen by `kind`: 0 silu(gate) * up, 1 the clamped form
+// above, 2 gelu(gate) * up in gelu's tanh form, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+template <typename TO>
+__global__ void gated_act_kernel(const float* gu, size_t n, int ff, int kind, float limit, float alpha,
+                                 int interleaved, TO* out) {
+  sb_pdl_launch();
+  sb_pdl_wait();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = e / ff, c = e % ff;
+    const size_t g = interleaved ? (c / SB_SWIGLU_BLOCK) * 2 * SB_SWIGLU_BLOCK + c % SB_SWIGLU_BLOCK : c;
+    const size_t u = interleaved ? g + SB_SWIGLU_BLOCK : ff + c;
+    const float gate = gu[r * 2 * ff + g], up = gu[r * 2 * ff + u];
+    out[e] = sb_from_f32<TO>(kind == 1 ? sb_glu_clamped(gate, up, limit, alpha)
+                                       : kind == 2 ? sb_gelu_tanh(gate) * up : sb_silu(gate) * up);
+  }
+}
+
+__global__ void scale_kernel(float* x, size_t n, float c) {
+  sb_pdl_launch();
+  sb_pdl_wait();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) x[e] *= c;
+}
+
 }  // namespace
 
 #define SB_DISPATCH_NEXT(has, code, TN, ...)  \
@@ -203,13 +232,13 @@ extern "C" int sb_norm_add(const float* y, const float* x, int n_rows, int width
                            float next_eps, void* normed, int normed_dtype, cudaStream_t stream) {
   if (n_rows <= 0 || width <= 0 || !y || !x || !w || !out)
     SB_FAIL(SB_ERR_ARG, "sb_norm_add: rows=%d width=%d", n_rows, width);
-  if (!sb_valid_dtype(w_dtype) || (normed && (!next_w || !sb_valid_dtype(next_w_dtype) || !sb_valid_dtype(normed_dtype))))
+  if (!sb_valid_dtype(w_dtype) || (normed && ((next_w && !sb_valid_dtype(next_w_dtype)) || !sb_valid_dtype(normed_dtype))))
     SB_FAIL(SB_ERR_ARG, "sb_norm_add: dtype codes %d %d %d", w_dtype, next_w_dtype, normed_dtype);
-  if (!(eps >= 0.0f) || (normed && !(next_eps >= 0.0f))) SB_FAIL(SB_ERR_ARG, "sb_norm_add: eps %g %g", eps, next_eps);
+  if (!(eps >= 0.0f) || (normed && next_w && !(next_eps >= 0.0f))) SB_FAIL(SB_ERR_ARG, "sb_norm_add: eps %g %g", eps, next_eps);
   const bool vec = width % 4 == 0 && (((uintptr_t)y | (uintptr_t)x | (uintptr_t)out) & 15) == 0;
   const bool wide = n_rows <= 256 && width >= 2048;
   SB_DISPATCH_DTYPE(w_dtype, TW, {
-    SB_DISPATCH_NEXT(normed, next_w_dtype, TN, {
+    SB_DISPATCH_NEXT(normed && next_w, next_w_dtype, TN, {
       SB_DISPATCH_NEXT(normed, normed_dtype, TO, {
         SB_ROW_LAUNCH(norm_add_kernel, TW, y, x, width, (const TW*)w, eps, out, (const TN*)next_w, next_eps, (TO*)normed);
       });
@@ -262,5 +291,31 @@ extern "C" int sb_glu_clamped(const float* gu, int n_rows, int ff, float limit, 
                                 interleaved, (TO*)out);
   });
   SB_CHECK_LAUNCH("sb_glu_clamped");
+  return SB_OK;
+}
+
+extern "C" int sb_gated_act(const float* gu, int n_rows, int ff, int kind, float limit, float alpha, int interleaved,
+                            void* out, int out_dtype, cudaStream_t stream) {
+  if (interleaved && ff % SB_SWIGLU_BLOCK)
+    SB_FAIL(SB_ERR_ARG, "sb_gated_act: %d outputs are no multiple of %d", ff, SB_SWIGLU_BLOCK);
+  if (n_rows <= 0 || ff <= 0 || !gu || !out) SB_FAIL(SB_ERR_ARG, "sb_gated_act: rows=%d ff=%d", n_rows, ff);
+  if (!sb_valid_dtype(out_dtype)) SB_FAIL(SB_ERR_ARG, "sb_gated_act: dtype code %d", out_dtype);
+  if (kind < SB_GATE_SILU || kind > SB_GATE_GELU_TANH || (kind == SB_GATE_CLAMPED && !(limit > 0.0f)))
+    SB_FAIL(SB_ERR_ARG, "sb_gated_act: kind %d, limit %g", kind, limit);
+  const size_t n = (size_t)n_rows * ff;
+  const int blocks = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+  SB_DISPATCH_DTYPE(out_dtype, TO, {
+    sb_launch<SB_K_ELEMENTWISE>(gated_act_kernel<TO>, dim3(blocks), dim3(256), 0, stream, gu, n, ff, kind, limit, alpha,
+                                interleaved, (TO*)out);
+  });
+  SB_CHECK_LAUNCH("sb_gated_act");
+  return SB_OK;
+}
+
+extern "C" int sb_scale(float* x, size_t n, float c, cudaStream_t stream) {
+  if (!x || n == 0) SB_FAIL(SB_ERR_ARG, "sb_scale: nothing to scale");
+  const int blocks = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+  sb_launch<SB_K_ELEMENTWISE>(scale_kernel, dim3(blocks), dim3(256), 0, stream, x, n, c);
+  SB_CHECK_LAUNCH("sb_scale");
   return SB_OK;
 }

@@ -175,6 +175,8 @@ class DecoderModel:
         hn = self.final_norm.forward(x, self.dtype, rows=plan.want_rows)
         logits = torch.empty((plan.n_want, s.vocab), dtype=torch.float32, device=self.device)
         ops.linear(hn, self.head, logits)
+        if s.logit_scale != 1.0:
+            ops.scale(logits, s.logit_scale)
         return ops.softcap(logits, s.logit_cap) if s.logit_cap > 0.0 else logits
 
 

@@ -141,18 +141,27 @@ def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
     return x
 
 
+def scale(x: torch.Tensor, c: float) -> torch.Tensor:
+    """x *= c in place (float32)."""
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(lib().sb_scale(_ptr(x), ctypes.c_size_t(x.numel()), ctypes.c_float(c), _stream()), "scale")
+    return x
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-            rows: torch.Tensor | None = None) -> torch.Tensor:
-    """out[r] = rmsnorm(x[rows[r]] or x[r]) * weight; x is the float32 residual stream."""
+            rows: torch.Tensor | None = None, width: int | None = None) -> torch.Tensor:
+    """out[r] = rmsnorm(x[rows[r]] or x[r]) * weight; x is the float32 residual stream.  With
+    `width`, only the first `width` values of every row of x are normed (and written)."""
     assert x.dtype == torch.float32 and x.dim() == 2
     n = out.shape[0]
-    width = x.shape[1]
-    assert out.shape[1] == width and weight.numel() == width
+    ld = x.shape[1]
+    width = ld if width is None else width
+    assert out.shape[1] == width and weight.numel() == width and width <= ld
     if rows is None:
         assert x.shape[0] == n
-    _check(lib().sb_rmsnorm(_ptr(x), _i32(rows, "rows") if rows is not None else _ptr(None), n,
-                            width, _ptr(weight), _code(weight.dtype), ctypes.c_float(eps),
-                            _ptr(out), _code(out.dtype), _stream()), "rmsnorm")
+    _check(lib().sb_rmsnorm_ld(_ptr(x), ld, _i32(rows, "rows") if rows is not None else _ptr(None), n,
+                               width, _ptr(weight), _code(weight.dtype), ctypes.c_float(eps),
+                               _ptr(out), _code(out.dtype), _stream()), "rmsnorm")
     return out
 
 
@@ -168,13 +177,17 @@ def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
            bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
            kernel: str = "auto", norm: tuple | None = None,
-           warm: torch.Tensor | None = None, gate: tuple | None = None) -> torch.Tensor:
+           warm: torch.Tensor | None = None, gate: tuple | None = None,
+           gate_kind: int = 0) -> torch.Tensor:
     """out = a @ w.T with a fused epilogue; a [M,K], w [N,K]; float32 accumulation.
 
     `gate` = (limit, slope) with EPI_SWIGLU makes the gated epilogue the clamped form
     a * sigmoid(slope a) * (b + 1), a = min(gate, limit), b = clamp(up, -limit, limit): inside the
     tcgen05 and the weight-streaming kernels where they run, else as the plain product followed
     by `glu_clamped`.
+
+    `gate_kind` = GATE_GELU_TANH with EPI_SWIGLU: gelu(gate) * up in gelu's tanh form, as the plain
+    product followed by `gated_act`.
 
     `norm` = (weight, eps, norm_out) also writes norm_out = rmsnorm(out, weight, eps) [M,N]
     (out must be float32): in the kernel that finishes the product where one does (the split-K
@@ -199,6 +212,11 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
         a = cast(a, torch.float32)
         if w.dtype != torch.float32:
             raise KernelError("linear: a float32 activation needs float32 weights")
+    if gate_kind == GATE_GELU_TANH:
+        assert epilogue == EPI_SWIGLU and N % (2 * SWIGLU_BLOCK) == 0 and gate is None
+        gu = torch.empty((M, N), dtype=torch.float32, device=a.device)
+        linear(a, w, gu, EPI_NONE, kernel=kernel)
+        return gated_act(gu, GATE_GELU_TANH, out, interleaved=True)
     if gate is not None:
         assert epilogue == EPI_SWIGLU and N % (2 * SWIGLU_BLOCK) == 0
         picked = kernel if kernel != "auto" else _pick_kernel(M, N, K, a.device)
@@ -481,9 +499,10 @@ def attention_lib(head_dim: int):
 def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache: torch.Tensor,
               n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, scale: float,
               kernel: str = "auto", warm: torch.Tensor | None = None,
-              sink: torch.Tensor | None = None) -> torch.Tensor:
+              sink: torch.Tensor | None = None, softcap: float = 0.0) -> torch.Tensor:
     """Causal grouped-query attention of the step's rows over one cache entry's pages.
     `sink` (float32, one per query head): exp(sink) joins that head's softmax denominator.
+    `softcap` c > 0: a score s becomes c tanh(s / c) before the softmax.
 
     bfloat16 runs the tensor-core kernels (built for the head size at first use); float32, a
     head size those kernels do not take, or `kernel="plain"` run the plain kernel.  `"mma"` keeps
@@ -511,7 +530,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
             head_dim, window, ctypes.c_float(scale), _ptr(scratch),
             ctypes.c_size_t(scratch.numel() if scratch is not None else 0),
             _ptr(counters), counters.numel(), plan.max_len, cache.shape[0], _sm_count(q.device),
-            *_warm_args(warm), _ptr(sink), _stream())
+            *_warm_args(warm), _ptr(sink), ctypes.c_float(softcap), _stream())
         if kernel in ("mma", "tma"):
             al.sb_attention_force_mma({"mma": 1, "tma": 2}.get(_os.environ.get("SB_ATTN", ""), 0))
         if rc != 0:
@@ -523,8 +542,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
             _ptr(q), _ptr(out), _code(q.dtype), n, _i32(plan.row_seq, "row_seq"),
             _i32(plan.row_pos, "row_pos"), _i32(g.page_off, "page_off"),
             _i32(g.page_ids, "page_ids"), g.page_size, _ptr(cache), _code(cache.dtype),
-            n_q_heads, n_kv_heads, head_dim, window, ctypes.c_float(scale), _ptr(sink), _stream()),
-            "attention (plain kernel)")
+            n_q_heads, n_kv_heads, head_dim, window, ctypes.c_float(scale), _ptr(sink),
+            ctypes.c_float(softcap), _stream()), "attention (plain kernel)")
     return out
 
 
@@ -614,7 +633,10 @@ def _next_norm_args(next_norm, width, rows):
     if next_norm is None:
         return _ptr(None), 0, ctypes.c_float(0.0), _ptr(None), 0
     w, eps, normed = next_norm
-    assert w.numel() == width and tuple(normed.shape) == (rows, width)
+    assert tuple(normed.shape) == (rows, width)
+    if w is None:                      # no norm: the finished rows as they are, in `normed`'s dtype
+        return _ptr(None), 0, ctypes.c_float(0.0), _ptr(normed), _code(normed.dtype)
+    assert w.numel() == width
     return _ptr(w), _code(w.dtype), ctypes.c_float(eps), _ptr(normed), _code(normed.dtype)
 
 
@@ -632,7 +654,8 @@ def _join_args(join, coef, rows, width):
 def norm_add(y: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
              next_norm: tuple | None = None) -> torch.Tensor:
     """out = x + y / sqrt(mean(y^2) + eps) * weight, row by row in float32 (out may be x).
-    `next_norm` = (weight, eps, normed) also writes the RMS norm of the finished rows."""
+    `next_norm` = (weight, eps, normed) also writes the RMS norm of the finished rows; with a
+    weight of None, `normed` receives the finished rows themselves in its own dtype."""
     rows, width = y.shape
     assert y.dtype == x.dtype == out.dtype == torch.float32 and x.shape == y.shape == out.shape
     assert weight.numel() == width
@@ -670,21 +693,46 @@ def glu_clamped(gate_up: torch.Tensor, limit: float, slope: float, out: torch.Te
     return out
 
 
+GATE_SILU, GATE_CLAMPED, GATE_GELU_TANH = 0, 1, 2
+GATE_KINDS = {"silu": GATE_SILU, "glu_clamped": GATE_CLAMPED, "gelu_tanh": GATE_GELU_TANH}
+
+
+def gated_act(gate_up: torch.Tensor, kind: int, out: torch.Tensor, interleaved: bool = False,
+              limit: float = 0.0, slope: float = 1.0) -> torch.Tensor:
+    """out = act(gate) * up over float32 rows [gate | up] (or, `interleaved`, blocks of SWIGLU_BLOCK
+    gates followed by the up values of the same outputs); `kind` is GATE_SILU, GATE_CLAMPED (the form
+    of `glu_clamped`, with `limit` and `slope`) or GATE_GELU_TANH (gelu in its tanh form)."""
+    rows, ff = out.shape
+    assert gate_up.dtype == torch.float32 and tuple(gate_up.shape) == (rows, 2 * ff)
+    _check(lib().sb_gated_act(_ptr(gate_up), rows, ff, int(kind), ctypes.c_float(limit), ctypes.c_float(slope),
+                              1 if interleaved else 0, _ptr(out), _code(out.dtype), _stream()), "gated_act")
+    return out
+
+
 # ---------------------------------------------------------------------- attention over a latent
 def latent_prep(proj: torch.Tensor, n_heads: int, dim: int, rot_dim: int, rank: int, rotary_dim: int,
                 inv_freq: torch.Tensor, row_seq, row_pos, page_off, page_ids, page_size: int,
                 cnorm: torch.Tensor | None, eps: float, cache: torch.Tensor | None,
-                q_wide: torch.Tensor, q_group: int = 0) -> torch.Tensor:
+                q_wide: torch.Tensor, q_group: int = 0, kv: tuple | None = None,
+                interleaved: bool = True, rot_scale: float = 1.0) -> torch.Tensor:
     """Finishes the fused projection rows [heads x (dim | rot_dim) | rank | rot_dim] (the last two
     only when `cache` is given): rotation in interleaved pairs, the latent's RMS norm, the cache
     write (key plane [latent | key part], value plane [latent | 0]), and every head's rotated
     part into q_wide[:, :, rank:].  With `q_group` (a divisor of the heads) q_wide lies
-    [head group, row, head in group, rank + rot_dim]."""
+    [head group, row, head in group, rank + rot_dim].  `kv` = (float32 rows, offset): the latent and
+    the key part [rank | rot_dim] start at `offset` of rows of their own (`proj` then holds the heads only).  Not `interleaved`: the pairs are (i, i + rotary_dim/2).
+    `rot_scale` multiplies every cosine and sine."""
     n = proj.shape[0]
     q_group = q_group or n_heads
     has_kv = cache is not None
     assert proj.dtype == torch.float32
-    assert proj.shape[1] == n_heads * (dim + rot_dim) + ((rank + rot_dim) if has_kv else 0)
+    assert proj.shape[1] == n_heads * (dim + rot_dim) + ((rank + rot_dim) if has_kv and kv is None else 0)
+    kv_ptr, kv_ld = None, 0
+    if kv is not None:
+        rows_kv, off = kv
+        assert has_kv and rows_kv.dtype == torch.float32 and rows_kv.is_contiguous() and rows_kv.shape[0] == n
+        assert off + rank + rot_dim <= rows_kv.shape[1]
+        kv_ptr, kv_ld = rows_kv.data_ptr() + 4 * off, rows_kv.shape[1]
     assert n_heads % q_group == 0 and q_wide.numel() == n * n_heads * (rank + rot_dim)
     assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= max(1, rotary_dim // 2)
     _check(lib().sb_latent_prep(
@@ -694,7 +742,8 @@ def latent_prep(proj: torch.Tensor, n_heads: int, dim: int, rot_dim: int, rank: 
         _i32(page_ids, "page_ids") if has_kv else _ptr(None), page_size,
         _ptr(cnorm) if has_kv else _ptr(None), _code(cnorm.dtype) if has_kv else 0, ctypes.c_float(eps),
         _ptr(cache), _code(cache.dtype) if has_kv else 0, _ptr(q_wide), _code(q_wide.dtype),
-        q_group, 1 if has_kv else 0, _stream()), "latent_prep")
+        q_group, 1 if has_kv else 0, kv_ptr, kv_ld, 1 if interleaved else 0,
+        ctypes.c_float(rot_scale), _stream()), "latent_prep")
     return q_wide
 
 
@@ -777,24 +826,32 @@ def attn_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, n_q_heads:
               dim: int, vdim: int, head_size: int, rotary_dim: int, interleaved: bool,
               inv_freq: torch.Tensor | None, v_inv_freq: torch.Tensor | None, q_norm: torch.Tensor | None,
               k_norm: torch.Tensor | None, eps: float, row_seq, row_pos, page_off, page_ids, page_size: int,
-              cache: torch.Tensor | None, q_out: torch.Tensor) -> torch.Tensor:
+              cache: torch.Tensor | None, q_out: torch.Tensor, head_norm: str | None = None,
+              rot_scale: float = 1.0) -> torch.Tensor:
     """Projection rows to queries and cache rows (see sb_attn_prep in the kernel library's header):
     optional RMS norm over the whole q and k projection, rotation in either layout of pairs,
     values that are the raw keys (`v_off` < 0), values rotated over their whole size (`v_inv_freq`),
-    heads padded with zeros to `head_size`.  `cache=None`: queries only."""
+    heads padded with zeros to `head_size`.  `cache=None`: queries only.
+    `head_norm` "before": every q and k head is RMS-normed by itself before the rotation, `q_norm` and
+    `k_norm` being one weight [dim] for all heads; "after": every head is divided by its root mean
+    square after the rotation (no weights).  `rot_scale` multiplies every cosine and sine."""
     n, ld = proj.shape
+    assert head_norm in (None, "before", "after")
     has_kv = cache is not None
     assert proj.dtype == torch.float32 and tuple(q_out.shape) == (n, n_q_heads, head_size)
     assert q_off + n_q_heads * dim <= ld and (not has_kv or k_off + n_kv_heads * dim <= ld)
     assert not has_kv or v_off < 0 or v_off + n_kv_heads * vdim <= ld
     assert rotary_dim == 0 or (inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2)
     assert v_inv_freq is None or (v_inv_freq.dtype == torch.float32 and v_inv_freq.numel() >= vdim // 2)
-    if q_norm is not None:
+    if q_norm is not None and head_norm == "before":
+        assert q_norm.dtype == k_norm.dtype and q_norm.numel() == k_norm.numel() == dim
+    elif q_norm is not None:
         assert q_norm.dtype == k_norm.dtype and q_norm.numel() == n_q_heads * dim and k_norm.numel() == n_kv_heads * dim
     _check(lib().sb_attn_prep(
         _ptr(proj), n, ld, q_off, k_off, v_off, n_q_heads, n_kv_heads, dim, vdim, head_size, rotary_dim,
         1 if interleaved else 0, _ptr(inv_freq), _ptr(v_inv_freq), _ptr(q_norm), _ptr(k_norm),
-        _code(q_norm.dtype) if q_norm is not None else 0, ctypes.c_float(eps),
+        _code(q_norm.dtype) if q_norm is not None else 0, {None: 0, "before": 1, "after": 2}[head_norm],
+        ctypes.c_float(rot_scale), ctypes.c_float(eps),
         _i32(row_seq, "row_seq"), _i32(row_pos, "row_pos"),
         _i32(page_off, "page_off") if has_kv else _ptr(None),
         _i32(page_ids, "page_ids") if has_kv else _ptr(None), page_size, _ptr(cache),
@@ -804,14 +861,21 @@ def attn_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, n_q_heads:
 
 
 def attn_unrotate(x: torch.Tensor, out: torch.Tensor, n_heads: int, head_size: int, vdim: int,
-                  interleaved: bool, v_inv_freq: torch.Tensor | None, row_pos) -> torch.Tensor:
+                  interleaved: bool, v_inv_freq: torch.Tensor | None, row_pos,
+                  gate: tuple | None = None) -> torch.Tensor:
     """out [rows, heads * vdim] = the first vdim values of every head of x [rows, heads * head_size],
-    turned back by the row's position when a table is given."""
+    turned back by the row's position when a table is given.  `gate` = (rows float32 [rows, ld],
+    offset): head h of a row is multiplied by sigmoid(rows[r, offset + h])."""
     n = out.shape[0]
+    g_ptr, g_ld = None, 0
+    if gate is not None:
+        g, off = gate
+        assert g.dtype == torch.float32 and g.is_contiguous() and g.shape[0] == n and off + n_heads <= g.shape[1]
+        g_ptr, g_ld = g.data_ptr() + 4 * off, g.shape[1]
     assert x.dtype == out.dtype and x.numel() == n * n_heads * head_size and out.shape[1] == n_heads * vdim
     _check(lib().sb_attn_unrotate(_ptr(x), _ptr(out), _code(x.dtype), n, n_heads, head_size, vdim,
-                                  1 if interleaved else 0, _ptr(v_inv_freq), _i32(row_pos, "row_pos"), _stream()),
-           "attn_unrotate")
+                                  1 if interleaved else 0, _ptr(v_inv_freq), _i32(row_pos, "row_pos"), g_ptr, g_ld,
+                                  _stream()), "attn_unrotate")
     return out
 
 
@@ -1032,6 +1096,23 @@ def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.
     assert logits.dtype == weights.dtype == torch.float32 and ids.dtype == torch.int32
     assert tuple(ids.shape) == tuple(weights.shape) == (n, top)
     _check(lib().sb_moe_route(_ptr(logits), n, e, top, _ptr(ids), _ptr(weights), _stream()), "moe_route")
+
+
+def moe_route_scored(logits: torch.Tensor, correction: torch.Tensor | None, top: int, ids: torch.Tensor,
+                     weights: torch.Tensor, groups: tuple = (1, 1), group_top: int = 2, scale: float = 1.0,
+                     renormalize: bool = False) -> None:
+    """Per row of float32 logits: scores s = sigmoid(logits); the `top` experts with the largest
+    choice scores s + correction (float32 [experts] or None; the lower index wins a tie) into ids, their
+    s * scale (over the chosen ones' sum of s first when `renormalize`) into weights.  `groups` =
+    (count, keep): the experts lie in `count` equal groups of neighbours, a group's score is the sum of
+    its `group_top` largest choice scores, and only experts of the `keep` best groups can be chosen."""
+    n, e = logits.shape
+    assert logits.dtype == weights.dtype == torch.float32 and ids.dtype == torch.int32
+    assert tuple(ids.shape) == tuple(weights.shape) == (n, top)
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == e)
+    _check(lib().sb_moe_route_scored(_ptr(logits), _ptr(correction), n, e, top, int(groups[0]), int(groups[1]),
+                                     int(group_top), ctypes.c_float(scale), 1 if renormalize else 0, _ptr(ids),
+                                     _ptr(weights), _stream()), "moe_route_scored")
 
 
 def moe_experts(h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_up: torch.Tensor,

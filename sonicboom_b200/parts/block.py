@@ -250,3 +250,90 @@ class ParallelResidualBlock(Block):
         x = self.mixer.forward(h, ctx, residual=x)
         ctx.next_norm, ctx.next_weights = after, after_weights
         return self.feed_forward.forward(h, ctx, residual=x)
+
+
+@register_block("output_norm")
+class OutputNormBlock(Block):
+    """No norm before a sublayer, an RMS norm on its result: x1 = x + m norm1(mix(x)); x2 = x1 + m
+    norm2(ffn(x1)) (without a feed-forward the result is x1).  The sublayers read the stream itself,
+    in the activation dtype; m (`params`: residual_mult) is folded into the norms' weights when they
+    are bound, in float32.  The normed result joins the stream in one kernel (`ops.norm_add`), which
+    also leaves behind what reads the finished rows next: the stream in the activation dtype for
+    this block's feed-forward or for a next block of this arrangement, or the next block's first
+    norm when that is a plain RMS norm."""
+
+    def __init__(self, spec, dtype, device):
+        from ..config.specs import ConfigError
+        from .norm import StreamCast
+        self.dtype = dtype
+        self.mult = float(dict(spec.params).get("residual_mult", 1.0))
+        self.mixer = make(MIXERS, "mixer", spec.mixer, dtype, device)
+        if spec.mixer_post_norm is None or (spec.feed_forward is not None and spec.feed_forward_post_norm is None):
+            raise ConfigError("an output_norm block needs a post norm for every sublayer it has")
+        self.mixer_post_norm = make(NORMS, "norm", spec.mixer_post_norm, dtype, device)
+        self.parts = [self.mixer, self.mixer_post_norm]
+        self.feed_forward = self.feed_forward_post_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward = make(FEED_FORWARDS, "feed-forward", spec.feed_forward, dtype, device)
+            self.feed_forward_post_norm = make(NORMS, "norm", spec.feed_forward_post_norm, dtype, device)
+            self.parts += [self.feed_forward, self.feed_forward_post_norm]
+        self.reads = StreamCast()         # what the mixer reads of the block's input
+        self.reads_again = StreamCast()   # what the feed-forward reads of x1
+        self.w1 = self.w2 = None
+
+    def tensor_requests(self):
+        return [r for p in self.parts for r in p.tensor_requests()]
+
+    def bind(self, get):
+        for p in self.parts:
+            p.bind(get)
+        for norm in (self.mixer_post_norm, self.feed_forward_post_norm):
+            if norm is not None and norm.as_rms() is None:
+                from ..config.specs import ConfigError
+                raise ConfigError("an output_norm block joins its sublayers through RMS norms")
+        self.w1 = (self.mixer_post_norm.as_rms()[0].float() * self.mult).contiguous()
+        if self.feed_forward is not None:
+            self.w2 = (self.feed_forward_post_norm.as_rms()[0].float() * self.mult).contiguous()
+
+    def kv_need(self):
+        return self.mixer.kv_need()
+
+    def state_need(self):
+        return self.mixer.state_need()
+
+    def input_norm(self):
+        return self.reads
+
+    def _read(self, cast, x, ctx):
+        h = ctx.take_normed(cast, x)
+        if h is not None or self.dtype == torch.float32:
+            return h if h is not None else x
+        return cast.forward(x, self.dtype)
+
+    def _join(self, y, x, w, eps, ctx, then):
+        """x += y / rms(y) * w in place; what reads x next is written along where it can be."""
+        from .norm import StreamCast
+        ride = None
+        if isinstance(then, StreamCast):
+            if self.dtype != torch.float32:
+                ride = (None, 0.0, torch.empty(x.shape, dtype=self.dtype, device=x.device))
+        elif then is not None and then.as_rms() is not None:
+            ride = (*then.as_rms(), torch.empty(x.shape, dtype=self.dtype, device=x.device))
+        ops.norm_add(y, x, w, eps, x, ride)
+        if ride is not None:
+            ctx.keep_normed(then, x, ride[2])
+        return x
+
+    def forward(self, x, ctx):
+        after, ctx.after_block_norm, ctx.after_block_weights = ctx.after_block_norm, None, None
+        h = self._read(self.reads, x, ctx)
+        ctx.next_norm = ctx.next_weights = None      # a post norm, not a norm of the stream, follows the product
+        y = self.mixer.forward(h, ctx)
+        eps1 = self.mixer_post_norm.as_rms()[1]
+        if self.feed_forward is None:
+            return self._join(y, x, self.w1, eps1, ctx, after)
+        x = self._join(y, x, self.w1, eps1, ctx, self.reads_again)
+        f = self._read(self.reads_again, x, ctx)
+        ctx.next_norm = ctx.next_weights = None
+        y = self.feed_forward.forward(f, ctx)
+        return self._join(y, x, self.w2, self.feed_forward_post_norm.as_rms()[1], ctx, after)

@@ -26,31 +26,48 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
+    """y = Wdown (act(Wgate f) * (Wup f)).  `activation` is "silu" or "gelu_tanh" (gelu in its tanh
+    form, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))); `params` may give `names`, the tensor
+    names of the three matrices after the prefix.  With silu the product's epilogue applies the
+    activation; with gelu_tanh the product's float32 rows go through the activation kernel."""
+
     def __init__(self, spec, dtype, device):
         from ..config.specs import ConfigError
         self.spec, self.dtype = spec, dtype
-        if spec.activation != "silu":
-            raise ConfigError(f"feed-forward activation {spec.activation!r} is not built (only silu)")
-        if spec.intermediate % ops.SWIGLU_BLOCK:
+        if spec.activation not in ("silu", "gelu_tanh"):
+            raise ConfigError(f"feed-forward activation {spec.activation!r} is not built (silu, gelu_tanh)")
+        self.interleaved = spec.intermediate % ops.SWIGLU_BLOCK == 0
+        if not self.interleaved and spec.activation == "silu":
             raise ConfigError(f"intermediate_size {spec.intermediate} must be a multiple of "
                               f"{ops.SWIGLU_BLOCK} for the fused gate/up product")
+        self.names = tuple(dict(spec.params).get("names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
         self.w_gate_up = self.w_down = None
 
     def tensor_requests(self):
         p, d, ff = self.spec.prefix, self.spec.width, self.spec.intermediate
-        return [TensorRequest(p + "gate_proj.weight", (ff, d)),
-                TensorRequest(p + "up_proj.weight", (ff, d)),
-                TensorRequest(p + "down_proj.weight", (d, ff))]
+        g, u, dn = self.names
+        return [TensorRequest(p + g, (ff, d)), TensorRequest(p + u, (ff, d)), TensorRequest(p + dn, (d, ff))]
 
     def bind(self, get):
         p = self.spec.prefix
-        self.w_gate_up = interleave_gate_up(get(p + "gate_proj.weight"), get(p + "up_proj.weight"))
-        self.w_down = get(p + "down_proj.weight")
+        g, u, dn = self.names
+        gate, up = get(p + g), get(p + u)
+        if gate.dtype != up.dtype:
+            gate, up = gate.float(), up.float()
+        self.w_gate_up = interleave_gate_up(gate, up) if self.interleaved else torch.cat([gate, up], dim=0).contiguous()
+        self.w_down = get(p + dn)
 
     def forward(self, h, ctx, residual=None):
-        rows = h.shape[0]
-        t = torch.empty((rows, self.spec.intermediate), dtype=self.dtype, device=h.device)
-        ops.linear(h, self.w_gate_up, t, ops.EPI_SWIGLU)
+        rows, ff = h.shape[0], self.spec.intermediate
+        t = torch.empty((rows, ff), dtype=self.dtype, device=h.device)
+        if self.spec.activation == "silu":
+            ops.linear(h, self.w_gate_up, t, ops.EPI_SWIGLU)
+        elif self.interleaved:
+            ops.linear(h, self.w_gate_up, t, ops.EPI_SWIGLU, gate_kind=ops.GATE_KINDS[self.spec.activation])
+        else:                                # other sizes keep [gate rows | up rows] and the activation kernel
+            gu = torch.empty((rows, 2 * ff), dtype=torch.float32, device=h.device)
+            ops.linear(h, self.w_gate_up, gu)
+            ops.gated_act(gu, ops.GATE_KINDS[self.spec.activation], t)
         out = residual if residual is not None else \
             torch.empty((rows, self.spec.width), dtype=torch.float32, device=h.device)
         return ctx.linear(t, self.w_down, out,
@@ -161,6 +178,12 @@ class ExpertsClampedGLU(FeedForward):
     [experts, width], router.b [experts], e<j>.gate, e<j>.up [intermediate, width], e<j>.down [width,
     intermediate]; the shared expert's under its own prefix.
 
+    With `router` = a dict, the choice is made on scores instead: s = sigmoid(z) (no bias), choice
+    scores s + a stored correction (`correction`: its tensor name), the experts in `groups` = (count,
+    keep) equal groups of neighbours of which only the `keep` best (by the sum of a group's `group_top`
+    largest choice scores) can be chosen, and the weights are the chosen experts' s times `scale`
+    (divided by their sum first when `renormalize`).
+
     The experts' matrices are stacked when bound, [experts, gate | up, intermediate, width] and
     [experts, width, intermediate]; a step groups its (token, choice) pairs by expert on the device
     and walks them in tiles of one expert, so no expert's matrix is read for tokens that did not
@@ -178,11 +201,21 @@ class ExpertsClampedGLU(FeedForward):
             raise ConfigError(f"feed-forward limit {self.limit} must be positive")
         shared = p.get("shared")
         self.shared = make(FEED_FORWARDS, "feed-forward", shared, dtype, device) if shared is not None else None
-        self.w_router = self.b_router = self.w_up = self.w_down = None
+        self.router = dict(p["router"]) if p.get("router") is not None else None
+        if self.router is not None:
+            count, keep = self.router.get("groups", (1, 1))
+            if count < 1 or self.n_experts % count or not 1 <= keep <= count or keep * (self.n_experts // count) < self.top:
+                raise ConfigError(f"{self.n_experts} experts in {count} groups of which {keep} are kept cannot "
+                                  f"give {self.top} choices")
+        self.w_router = self.b_router = self.w_up = self.w_down = self.correction = None
 
     def tensor_requests(self):
         p, d, ff = self.spec.prefix, self.spec.width, self.spec.intermediate
-        req = [TensorRequest(p + "router", (self.n_experts, d)), TensorRequest(p + "router.b", (self.n_experts,), "bias")]
+        req = [TensorRequest(p + "router", (self.n_experts, d))]
+        if self.router is None:
+            req.append(TensorRequest(p + "router.b", (self.n_experts,), "bias"))
+        elif self.router.get("correction"):
+            req.append(TensorRequest(p + self.router["correction"], (self.n_experts,), "bias"))
         for j in range(self.n_experts):
             req += [TensorRequest(f"{p}e{j}.gate", (ff, d)), TensorRequest(f"{p}e{j}.up", (ff, d)),
                     TensorRequest(f"{p}e{j}.down", (d, ff))]
@@ -190,7 +223,11 @@ class ExpertsClampedGLU(FeedForward):
 
     def bind(self, get):
         p = self.spec.prefix
-        self.w_router, self.b_router = get(p + "router"), get(p + "router.b")
+        self.w_router = get(p + "router")
+        if self.router is None:
+            self.b_router = get(p + "router.b")
+        elif self.router.get("correction"):
+            self.correction = get(p + self.router["correction"]).float().contiguous()
         ups = [torch.stack([get(f"{p}e{j}.gate"), get(f"{p}e{j}.up")]) for j in range(self.n_experts)]
         downs = [get(f"{p}e{j}.down") for j in range(self.n_experts)]
         kept = {t.dtype for t in ups + downs}
@@ -205,10 +242,17 @@ class ExpertsClampedGLU(FeedForward):
         # what follows this part follows its last kernel, which is not a product: nothing rides on one
         ctx.next_norm = ctx.next_weights = None
         logits = torch.empty((rows, self.n_experts), dtype=torch.float32, device=h.device)
-        ops.linear(h, self.w_router, logits, ops.EPI_BIAS, bias=self.b_router)
         ids = torch.empty((rows, self.top), dtype=torch.int32, device=h.device)
         weights = torch.empty((rows, self.top), dtype=torch.float32, device=h.device)
-        ops.moe_route(logits, self.top, ids, weights)
+        if self.router is None:
+            ops.linear(h, self.w_router, logits, ops.EPI_BIAS, bias=self.b_router)
+            ops.moe_route(logits, self.top, ids, weights)
+        else:
+            r = self.router
+            ops.linear(h, self.w_router, logits)
+            ops.moe_route_scored(logits, self.correction, self.top, ids, weights, groups=r.get("groups", (1, 1)),
+                                 group_top=int(r.get("group_top", 2)), scale=float(r.get("scale", 1.0)),
+                                 renormalize=bool(r.get("renormalize", False)))
         if self.shared is not None:
             out = self.shared.forward(h, ctx, residual=residual)
         elif residual is not None:

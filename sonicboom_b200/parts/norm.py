@@ -77,3 +77,14 @@ class LayerNorm(Norm):
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.width), dtype=out_dtype, device=x.device)
         return ops.layernorm(x, self.weight, self.eps, out, rows)
+
+
+class StreamCast(Norm):
+    """Not a norm: the rows as they are, in the dtype asked for.  A block whose sublayers read the
+    stream itself names this as its `input_norm()`, so that whatever finishes the stream's rows
+    before it (`ops.norm_add` with a weight of None) can leave the copy behind."""
+
+    def forward(self, x, out_dtype, rows=None):
+        if rows is not None:
+            raise NotImplementedError("a stream cast gathers no rows")
+        return ops.cast(x, out_dtype)

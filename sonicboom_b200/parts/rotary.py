@@ -83,3 +83,53 @@ class RotaryHalves(PositionEncoding):
             raise ConfigError(f"rotary_dim {self.rotary_dim} must be even and at most the rotated "
                               f"vector's length {self.head_dim}")
         self.inv_freq = frequency_table(spec.theta, self.rotary_dim, device)
+
+
+YARN_MAGNITUDE_SLOPE = 0.1      # cosines and sines grow by 0.1 ln(factor) + 1
+YARN_RAMP_FLOOR = 0.001         # the ramp's length is at least this
+
+
+def yarn_frequencies(base: float, n: int, factor: float, original: float, fast: float, slow: float):
+    """(float64 [n/2] frequencies, magnitude) of a rotation whose slow pairs are stretched.
+    f_i = base^(-2i/n).  With dim(t) = n ln(original / (2 pi t)) / (2 ln base), the pair number at which
+    a pair makes t turns over `original` positions, lo = max(floor(dim(fast)), 0), hi =
+    min(ceil(dim(slow)), n - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i
+    turns with f_i / factor * ramp_i + f_i * (1 - ramp_i): fast pairs keep their frequency, slow
+    ones are divided by `factor`, those between are blended.  Cosines and sines are multiplied by
+    0.1 ln(factor) + 1."""
+    import math
+    i = np.arange(max(1, n // 2), dtype=np.float64)
+    f = np.power(np.float64(base), -2.0 * i / np.float64(max(n, 1)))
+
+    def pair_at(turns):
+        return n * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+    lo = max(math.floor(pair_at(fast)), 0)
+    hi = min(math.ceil(pair_at(slow)), n - 1)
+    ramp = np.clip((i - lo) / max(hi - lo, YARN_RAMP_FLOOR), 0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), YARN_MAGNITUDE_SLOPE * math.log(factor) + 1.0
+
+
+@register_position_encoding("rope_halves_yarn")
+class RotaryHalvesYarn(PositionEncoding):
+    """"rope_halves" with stretched slow pairs (`yarn_frequencies`).  `params`: factor, original,
+    fast, slow.  `magnitude` multiplies every cosine and sine; the kernels that rotate take it as
+    their `rot_scale`."""
+    layout = "halves"
+
+    def __init__(self, spec, dtype, device):
+        from ..config.specs import ConfigError
+        self.head_dim = spec.head_dim
+        self.rotary_dim = spec.rotary_dim
+        if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
+            raise ConfigError(f"rotary_dim {self.rotary_dim} must be even and at most the rotated "
+                              f"vector's length {self.head_dim}")
+        p = dict(spec.params)
+        try:
+            factor, original = float(p["factor"]), float(p["original"])
+            fast, slow = float(p["fast"]), float(p["slow"])
+        except KeyError as e:
+            raise ConfigError(f"a stretched rotation needs the parameter {e.args[0]}") from None
+        if not (factor > 0 and original > 0 and fast > 0 and slow > 0):
+            raise ConfigError("a stretched rotation's factor, original, fast and slow must be positive")
+        freq, self.magnitude = yarn_frequencies(spec.theta, self.rotary_dim, factor, original, fast, slow)
+        self.inv_freq = torch.from_numpy(freq.astype(np.float32)).to(device)

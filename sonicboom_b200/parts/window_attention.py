@@ -14,7 +14,15 @@ that attention layers of newer designs combine:
   pairs, frequencies base^(-2m/vdim)) before it is cached, and every head's result at position i
   is turned back by i: what a head sums depends on i - j only;
 * `sink` = name: one learned number per query head whose exponential joins the softmax's
-  denominator (it has no key, no value and is not scaled).
+  denominator (it has no key, no value and is not scaled);
+* `bias` = (q name, k name, v name): the three projections have biases;
+* `head_norm` = ("before", q name, k name): every q and k head is RMS-normed by itself before the
+  rotation, with one weight of head_dim values for all heads; ("after",): every head is divided by
+  its root mean square after the rotation, without a weight;
+* `softcap` = c: a score s becomes c tanh(s / c) before the softmax;
+* `gate` = name: a matrix [heads, width]; head h's result is multiplied by the logistic function
+  of its product with the mixer's input (it rides on the input product);
+* a position encoding with a `magnitude` (stretched rotations) multiplies cosines and sines by it.
 
 Tensors after the prefix: q [heads*head_dim, width], k [kv_heads*head_dim, width], v
 [kv_heads*vdim, width] unless the values are the keys, o [width, heads*vdim], and what the options
@@ -47,6 +55,17 @@ class WindowAttention(Mixer):
         self.values_are_keys = p.get("values", "own") == "keys"
         self.rotate_values = bool(p.get("rotate_values", False))
         self.qk_norm, self.sink_name = p.get("qk_norm"), p.get("sink")
+        self.bias_names, self.gate_name = p.get("bias"), p.get("gate")
+        self.softcap = float(p.get("softcap", 0.0) or 0.0)
+        head_norm = p.get("head_norm")
+        self.head_norm = head_norm[0] if head_norm else None
+        if self.head_norm not in (None, "before", "after") or (self.head_norm and self.qk_norm):
+            raise ConfigError(f"head_norm {head_norm!r}: ('before', q name, k name) or ('after',), and not "
+                              "beside a norm of the whole projection")
+        if self.head_norm == "before":
+            self.qk_norm = tuple(head_norm[1:3])
+        if self.softcap < 0.0:
+            raise ConfigError(f"a score cap of {self.softcap} (0: none)")
         self.names = tuple(p.get("names", ("q", "k", "v", "o")))
         if self.hq % self.hkv:
             raise ConfigError(f"{self.hq} query heads are not a multiple of {self.hkv} key/value heads")
@@ -58,8 +77,10 @@ class WindowAttention(Mixer):
             raise ConfigError("rotated values take their frequencies' base from the position encoding")
         self.hd = (max(self.dim, self.vdim) + HEAD_STEP - 1) // HEAD_STEP * HEAD_STEP
         self.rot, self.interleaved, self.inv_freq, self.v_inv_freq = 0, False, None, None
+        self.rot_scale = 1.0
         if spec.position is not None:
             pe = make(POSITION_ENCODINGS, "position encoding", spec.position, dtype, device)
+            self.rot_scale = float(getattr(pe, "magnitude", 1.0))
             self.interleaved = getattr(pe, "layout", "halves") == "interleaved"
             self.rot = spec.position.rotary_dim
             self.inv_freq = pe.inv_freq if self.rot > 0 else None
@@ -67,7 +88,10 @@ class WindowAttention(Mixer):
                 self.v_inv_freq = frequency_table(spec.position.theta, self.vdim, device)
         self.qw, self.kw = self.hq * self.dim, self.hkv * self.dim
         self.vw = 0 if self.values_are_keys else self.hkv * self.vdim
-        self.w_in = self.w_o = self.q_norm = self.k_norm = self.sink = None
+        self.gw = self.hq if self.gate_name else 0
+        if self.bias_names and self.values_are_keys:
+            raise ConfigError("biases of q, k and v need a value projection of its own")
+        self.w_in = self.w_o = self.q_norm = self.k_norm = self.sink = self.b_in = None
 
     def kv_need(self):
         return KVNeed(self.hkv, self.hd, self.spec.window)
@@ -80,8 +104,13 @@ class WindowAttention(Mixer):
         if not self.values_are_keys:
             req.append(TensorRequest(p + v, (self.hkv * self.vdim, d)))
         if self.qk_norm:
-            req += [TensorRequest(p + self.qk_norm[0], (self.qw,), "norm"),
-                    TensorRequest(p + self.qk_norm[1], (self.kw,), "norm")]
+            per_head = self.head_norm == "before"
+            req += [TensorRequest(p + self.qk_norm[0], (self.dim if per_head else self.qw,), "norm"),
+                    TensorRequest(p + self.qk_norm[1], (self.dim if per_head else self.kw,), "norm")]
+        if self.bias_names:
+            req += [TensorRequest(p + n, (w,), "bias") for n, w in zip(self.bias_names, (self.qw, self.kw, self.vw))]
+        if self.gate_name:
+            req.append(TensorRequest(p + self.gate_name, (self.hq, d)))
         if self.sink_name:
             req.append(TensorRequest(p + self.sink_name, (self.hq,), "bias"))
         return req
@@ -89,7 +118,13 @@ class WindowAttention(Mixer):
     def bind(self, get):
         p = self.spec.prefix
         q, k, v, o = self.names
-        self.w_in = _cat([get(p + n) for n in ((q, k) if self.values_are_keys else (q, k, v))])
+        # rows of the one input product: [q | gate | k | v]; an entry that reads another's cache stops after the gate
+        names = [q] + ([self.gate_name] if self.gate_name else []) + ([k] if self.values_are_keys else [k, v])
+        self.w_in = _cat([get(p + n) for n in names])
+        if self.bias_names:
+            bq, bk, bv = (get(p + n).float() for n in self.bias_names)
+            zero = [torch.zeros(self.gw, dtype=torch.float32, device=bq.device)] if self.gw else []
+            self.b_in = torch.cat([bq] + zero + [bk, bv]).contiguous()
         self.w_o = get(p + o)
         if self.qk_norm:
             self.q_norm, self.k_norm = get(p + self.qk_norm[0]), get(p + self.qk_norm[1])
@@ -105,23 +140,28 @@ class WindowAttention(Mixer):
 
     def forward(self, h, ctx, residual=None):
         rows, plan = h.shape[0], ctx.plan
-        width_in = self.qw + ((self.kw + self.vw) if ctx.owns_cache else 0)
+        k_off = self.qw + self.gw
+        width_in = k_off + ((self.kw + self.vw) if ctx.owns_cache else 0)
         storage = ctx.kv_storage()
         g = plan.groups[ctx.kv_group()]
         proj = torch.empty((rows, width_in), dtype=torch.float32, device=h.device)
-        ops.linear(h, self.w_in[:width_in], proj)
+        if self.b_in is not None:
+            ops.linear(h, self.w_in[:width_in], proj, ops.EPI_BIAS, bias=self.b_in[:width_in])
+        else:
+            ops.linear(h, self.w_in[:width_in], proj)
         q = torch.empty((rows, self.hq, self.hd), dtype=self.dtype, device=h.device)
-        ops.attn_prep(proj, 0, self.qw, -1 if self.values_are_keys else self.qw + self.kw, self.hq, self.hkv,
+        ops.attn_prep(proj, 0, k_off, -1 if self.values_are_keys else k_off + self.kw, self.hq, self.hkv,
                       self.dim, self.vdim, self.hd, self.rot, self.interleaved, self.inv_freq, self.v_inv_freq,
                       self.q_norm, self.k_norm, self.eps, plan.row_seq, plan.row_pos, g.page_off, g.page_ids,
-                      g.page_size, storage if ctx.owns_cache else None, q)
+                      g.page_size, storage if ctx.owns_cache else None, q, head_norm=self.head_norm,
+                      rot_scale=self.rot_scale)
         mixed = torch.empty((rows, self.hq * self.hd), dtype=self.dtype, device=h.device)
         ops.attention(q, mixed, plan, ctx.kv_group(), storage, self.hq, self.hkv, self.hd, self.spec.window,
-                      self.spec.scale, warm=self.w_o, sink=self.sink)
-        if self.rotate_values or self.hd != self.vdim:
+                      self.spec.scale, warm=self.w_o, sink=self.sink, softcap=self.softcap)
+        if self.rotate_values or self.hd != self.vdim or self.gw:
             turned = torch.empty((rows, self.hq * self.vdim), dtype=self.dtype, device=h.device)
             mixed = ops.attn_unrotate(mixed, turned, self.hq, self.hd, self.vdim, self.interleaved,
-                                      self.v_inv_freq, plan.row_pos)
+                                      self.v_inv_freq, plan.row_pos, gate=(proj, self.qw) if self.gw else None)
         out = residual if residual is not None else \
             torch.empty((rows, self.spec.width), dtype=torch.float32, device=h.device)
         return ctx.linear(mixed, self.w_o, out, ops.EPI_RESIDUAL if residual is not None else ops.EPI_NONE,

@@ -57,17 +57,14 @@ def frequencies(rot):
 def rotate(x, positions, rot):
     """x [T, heads, d]: the first rot.dims values of every head turn, pair (i, i + dims/2)."""
     n = rot["dims"]
+    if n == 0:
+        return x.clone()
     f, mag = frequencies(rot)
     half = n // 2
-    out = x.clone()
-    for t, p in enumerate(positions):
-        for i in range(half):
-            a = p * f[i]
-            c, s = math.cos(a) * mag, math.sin(a) * mag
-            u, v = x[t, :, i], x[t, :, i + half]
-            out[t, :, i] = u * c - v * s
-            out[t, :, i + half] = v * c + u * s
-    return out
+    a = torch.tensor(list(positions), dtype=F).view(-1, 1, 1) * torch.tensor(f, dtype=F).view(1, 1, half)
+    c, s = torch.cos(a) * mag, torch.sin(a) * mag
+    u, v = x[:, :, :half], x[:, :, half:n]
+    return torch.cat([u * c - v * s, v * c + u * s, x[:, :, n:]], dim=-1)
 
 
 def softmax_rows(scores, visible, sink=None):
@@ -143,14 +140,15 @@ def attention_2(h, get, m, eps):
     v = (h @ get("v").T).view(T, G, dv)
     pos = list(range(T))
     q, k = rms(rotate(q, pos, m["rot"]), eps), rms(rotate(k, pos, m["rot"]), eps)
-    cap = m["softcap"]
-    vis = causal(T, m["mask"]["size"])
+    cap = m.get("softcap") or 0.0
+    vis = causal(T, m["mask"]["size"] if m.get("mask") else 0)
     gate = torch.sigmoid(h @ get("g").T)
     out = torch.zeros(T, H, dv, dtype=F)
     for hh in range(H):
         g = hh // (H // G)
         s = (q[:, hh] @ k[:, g].T) * m["scale"]
-        s = cap * torch.tanh(s / cap)
+        if cap:
+            s = cap * torch.tanh(s / cap)
         out[:, hh] = (softmax_rows(s, vis) @ v[:, g]) * gate[:, hh:hh + 1]
     return out.reshape(T, H * dv) @ get("o").T
 
@@ -195,12 +193,17 @@ def moe_ff(h, get, mlp, gaps=None):
     r = mlp["router"]
     z = h @ get("router").T
     out = torch.zeros(T, h.shape[1], dtype=F)
+    sent = {}                                   # expert -> [(token, weight)]
     for t in range(T):
         chosen, weights, gap = route(z[t], get("correction"), r)
         if gaps is not None:
             gaps.append(gap)
         for e, w in zip(chosen, weights):
-            out[t] += w * expert(h[t:t + 1], lambda n, e=e: get(f"e{e}.{n}"), mlp["expert"]["limit"])[0]
+            sent.setdefault(e, []).append((t, w))
+    for e, pairs in sent.items():
+        rows = torch.tensor([t for t, _ in pairs])
+        y = expert(h[rows], lambda n, e=e: get(f"e{e}.{n}"), mlp["expert"]["limit"])
+        out[rows] += torch.tensor([w for _, w in pairs], dtype=F).view(-1, 1) * y
     if mlp.get("shared") is not None:
         out = out + expert(h, lambda n: get("shared." + n), mlp["shared"]["limit"])
     return out
@@ -230,3 +233,11 @@ def forward(cfg, tensors, tokens, layers_out=None, gaps=None):
         if layers_out is not None:
             layers_out.append(x.clone())
     return (rms(x, eps) * W["final.norm"]) @ W["head"].T * cfg["logit_scale"]
+
+
+def greedy_generate(cfg, tensors, prompt, n_new):
+    seq, out = list(prompt), []
+    for _ in range(n_new):
+        out.append(int(torch.argmax(forward(cfg, tensors, seq)[-1])))
+        seq.append(out[-1])
+    return out

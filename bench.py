@@ -6,6 +6,7 @@ sizes of Qwen2.5-7B with random weights on one B200.
     python bench.py --arch zolulix [--sizes w2048,w3584] [--prompt 2048] [--batch 8] [--steps K]
     python bench.py --arch mefupel [--sizes w2048,w3584] [--prompt 2048] [--batch 8] [--steps K]
     python bench.py --arch leguvik [--sizes w2048,w3584] [--prompt 2048] [--batch 8] [--steps K]
+    python bench.py --arch bulodra [--sizes w2048,w3584] [--prompt 2048] [--batch 8] [--steps K]
 
 Prints ONE JSON line.  (`--arch zolulix` is a measurement of its own: the Zolulix design beside the
 Qwen2.5 decoder of equal sizes and its kernels alone; without it the workload below runs.)  A "step" is one decode step of the whole batch.  The default run is a
@@ -981,6 +982,214 @@ def run_leguvik(args) -> int:
     print(json.dumps(result))
     return 0
 
+# ---------------------------------------------------------------------------- --arch bulodra
+def bulodra_config(width, n_layers, vocab, heads, kv_heads, dim, window, l_dim, l_rot, l_vdim, kv_rank, q_rank,
+                   experts, top, groups, expert_ff, shared_ff, dense_ff):
+    """A Bulodra model of the given layer sizes: attention over a latent, two capped attentions in a
+    window, one attention with a sink, and so on in turn; the first layer with a dense feed-forward,
+    the others with a mixture of experts in groups and a shared expert."""
+    yarn = {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+    kinds = [("latent_attention", {"heads": heads, "dim": l_dim, "rot_dim": l_rot, "vdim": l_vdim, "kv_rank": kv_rank,
+                                   "q_rank": q_rank, "scale": (l_dim + l_rot) ** -0.5,
+                                   "rot": {"base": 1e6, "dims": l_rot, "scaling": yarn}}),
+             ("attention_2", {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                              "softcap": 30.0, "mask": {"size": window}, "rot": {"base": 5e5, "dims": dim // 2}}),
+             ("attention_2", {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                              "softcap": 30.0, "mask": {"size": window}, "rot": {"base": 5e5, "dims": dim // 2}}),
+             ("attention", {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                            "rot": {"base": 5e5, "dims": dim, "scaling": yarn}})]
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.5,
+                                     "groups": {"count": groups[0], "keep": groups[1]}},
+           "expert": {"ff": expert_ff, "limit": 7.0}, "shared": {"ff": shared_ff, "limit": 7.0}}
+    layers = [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1],
+               "mlp": {"kind": "dense", "ff": dense_ff} if i == 0 else moe} for i in range(n_layers)]
+    return {"architecture": "Bulodra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "logit_scale": 0.25, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 36313, "mul_cur": 27191}},
+            "layers": layers}
+
+
+BULODRA_SIZES = {
+    # name: Bulodra sizes; the Leguvik model beside it (the closest design: a mixture of clamped gated
+    # experts with a shared expert, windowed attention with a score cap, the pair embedding) has the
+    # same width, depth, vocabulary, attention heads and window, experts, choices and expert sizes
+    "w2048": dict(width=2048, n_layers=8, vocab=32768, heads=16, kv_heads=4, dim=128, window=1024, l_dim=64, l_rot=32,
+                  l_vdim=64, kv_rank=96, q_rank=512, experts=32, top=4, groups=(4, 2), expert_ff=1024, shared_ff=2048,
+                  dense_ff=8192),
+    "w3584": dict(width=3584, n_layers=8, vocab=32768, heads=28, kv_heads=4, dim=128, window=4096, l_dim=96, l_rot=32,
+                  l_vdim=128, kv_rank=224, q_rank=768, experts=64, top=6, groups=(8, 4), expert_ff=1536, shared_ff=3072,
+                  dense_ff=18944),
+}
+
+
+def bulodra_kernels(bench, z, rows, context):
+    """Each kernel that came with Bulodra (or was extended for it) alone at `rows` rows (one sequence
+    of `rows` tokens when rows > 64, else `rows` sequences that hold `context` tokens each and go on
+    by one), with the bytes it must read and write once, and beside each the like kernel of the
+    framework's other models at the same sizes."""
+    import torch
+    from sonicboom_b200 import ops
+    from sonicboom_b200.cache.kv import Cache, KVNeed
+    from sonicboom_b200.engine.step import StepEntry, StepPlan
+    from sonicboom_b200.parts.rotary import frequency_table
+    dev, pk, timed = bench.dev, bench.pk, bench.timed
+    W = z["width"]
+    f32, bf = torch.float32, torch.bfloat16
+    out = {}
+
+    def rec(name, ms, nbytes, flops=0):
+        out[name] = {"us": round(ms * 1e3, 2), "bytes": int(nbytes),
+                     "hbm_frac": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 3)}
+        if flops:
+            out[name]["tflops"] = round(flops / (ms / 1e3) / 1e12, 2)
+    prompt = rows > 64
+    n_seqs, new = (1, rows) if prompt else (rows, 1)
+    past = 0 if prompt else context
+    H, G, d, win = z["heads"], z["kv_heads"], z["dim"], z["window"]
+    ld, lr, lv, rank, qr = z["l_dim"], z["l_rot"], z["l_vdim"], z["kv_rank"], z["q_rank"]
+    wide = rank + lr
+    cache = Cache([KVNeed(G, d, win), KVNeed(1, wide, 0)], [None, None], n_seqs * (past + new + 64), bf, dev,
+                  n_slots=n_seqs)
+    slots = [cache.open() for _ in range(n_seqs)]
+    for s in slots:
+        if past:
+            cache.reserve(s, past)
+            cache.advance(s, past)
+        cache.reserve(s, past + new)
+    plan = StepPlan(cache, [StepEntry(s, [0] * new, []) for s in slots], dev)
+    kind = f"{n_seqs} sequence(s) of {new}" + (f" after {past}" if past else "")
+    # rows of the stream
+    x, y = torch.randn(rows, W, device=dev), torch.randn(rows, W, device=dev)
+    wn = torch.ones(W, device=dev)
+    wb = torch.ones(W, device=dev, dtype=bf)
+    xo, nb = torch.empty(rows, W, device=dev), torch.empty(rows, W, device=dev, dtype=bf)
+    rec("norm_add + the stream in bfloat16", timed(lambda: ops.norm_add(y, x, wn, 1e-6, xo, (None, 0.0, nb))), rows * W * 14)
+    rec("like: norm_add + next norm", timed(lambda: ops.norm_add(y, x, wn, 1e-6, xo, (wb, 1e-6, nb))), rows * W * 14)
+    # queries and cache rows
+    g0, store0 = plan.groups[cache.group_of_entry[0]], cache.groups[cache.group_of_entry[0]].entry_storage(0)
+    g1, store1 = plan.groups[cache.group_of_entry[1]], cache.groups[cache.group_of_entry[1]].entry_storage(1)
+    store0.normal_()
+    store1.normal_()
+    n_in = (H + 2 * G) * d + H
+    proj = torch.randn(rows, n_in, device=dev)
+    q = torch.empty(rows, H, d, device=dev, dtype=bf)
+    table = frequency_table(5e5, d, dev)
+    hw, kw = torch.ones(d, device=dev, dtype=bf), torch.ones(d, device=dev, dtype=bf)
+    prep_bytes = rows * ((H + 2 * G) * d * 4 + (H + 2 * G) * d * 2)
+
+    def prep(head_norm, qn, kn, rot):
+        return lambda: ops.attn_prep(proj, 0, H * d + H, H * d + H + G * d, H, G, d, d, d, rot, False, table, None, qn, kn,
+                                     1e-6, plan.row_seq, plan.row_pos, g0.page_off, g0.page_ids, g0.page_size, store0,
+                                     q, head_norm=head_norm, rot_scale=1.2)
+    rec("attn_prep, every head normed before the rotation", timed(prep("before", hw, kw, d)), prep_bytes)
+    rec("attn_prep, every head normed after the rotation", timed(prep("after", None, None, d // 2)), prep_bytes)
+    qn_all, kn_all = torch.ones(H * d, device=dev, dtype=bf), torch.ones(G * d, device=dev, dtype=bf)
+    rec("like: attn_prep, the whole projection normed", timed(prep(None, qn_all, kn_all, d)), prep_bytes)
+    rec("like: attn_prep, no norm", timed(prep(None, None, None, d)), prep_bytes)
+    # attention with a score cap
+    o = torch.empty(rows, H * d, device=dev, dtype=bf)
+    if prompt:
+        keys = sum(min(i + 1, win) for i in range(rows))
+        kv_bytes = rows * G * d * 4
+    else:
+        keys = rows * min(past + 1, win)
+        kv_bytes = keys * G * d * 4
+    att_bytes, att_flops = kv_bytes + rows * H * d * 4, 4 * keys * H * d
+    grp0 = cache.group_of_entry[0]
+    rec(f"attention, capped scores ({kind}; window {win})",
+        timed(lambda: ops.attention(q, o, plan, grp0, store0, H, G, d, win, d ** -0.5, softcap=30.0)), att_bytes, att_flops)
+    rec(f"like: attention ({kind}; window {win})",
+        timed(lambda: ops.attention(q, o, plan, grp0, store0, H, G, d, win, d ** -0.5)), att_bytes, att_flops)
+    sink = torch.zeros(H, device=dev)
+    rec(f"like: attention with a sink ({kind}; window {win})",
+        timed(lambda: ops.attention(q, o, plan, grp0, store0, H, G, d, win, d ** -0.5, sink=sink)), att_bytes, att_flops)
+    # the gate on every head's result
+    og = torch.empty(rows, H * d, device=dev, dtype=bf)
+    rec("attn_unrotate with the heads' gates", timed(lambda: ops.attn_unrotate(o, og, H, d, d, False, None, plan.row_pos,
+                                                                               gate=(proj, H * d))), rows * H * d * 4)
+    o_pad = torch.empty(rows, H * (d + 16), device=dev, dtype=bf)
+    rec("like: attn_unrotate (padding dropped)", timed(lambda: ops.attn_unrotate(o_pad, og, H, d + 16, d, False, None,
+                                                                                plan.row_pos)), rows * H * d * 4)
+    # the latent's rows
+    first = torch.randn(rows, qr + wide, device=dev)
+    cq = torch.empty(rows, qr, device=dev, dtype=bf)
+    wq = torch.ones(qr, device=dev, dtype=bf)
+    rec("rmsnorm of a row's first values (the query latent)", timed(lambda: ops.rmsnorm(first, wq, 1e-6, cq, width=qr)),
+        rows * qr * 6)
+    flat = torch.randn(rows, qr, device=dev)
+    rec("like: rmsnorm", timed(lambda: ops.rmsnorm(flat, wq, 1e-6, cq)), rows * qr * 6)
+    lproj = torch.randn(rows, H * (ld + lr), device=dev)
+    qwide = torch.empty(1, rows, H, wide, device=dev, dtype=bf)
+    cn = torch.ones(rank, device=dev, dtype=bf)
+    ltab = frequency_table(1e6, lr, dev)
+    lbytes = rows * (H * lr * 6 + wide * 4 + wide * 4)
+    rec("latent_prep, pairs half the part apart, the latent in rows of its own",
+        timed(lambda: ops.latent_prep(lproj, H, ld, lr, rank, lr, ltab, plan.row_seq, plan.row_pos, g1.page_off, g1.page_ids,
+                                      g1.page_size, cn, 1e-6, store1, qwide, H, kv=(first, qr), interleaved=False,
+                                      rot_scale=1.2)), lbytes)
+    lboth = torch.randn(rows, H * (ld + lr) + wide, device=dev)
+    rec("like: latent_prep, interleaved pairs, one row",
+        timed(lambda: ops.latent_prep(lboth, H, ld, lr, rank, lr, ltab, plan.row_seq, plan.row_pos, g1.page_off, g1.page_ids,
+                                      g1.page_size, cn, 1e-6, store1, qwide, H)), lbytes)
+    # the router and the dense feed-forward's gate
+    E, top = z["experts"], z["top"]
+    logits = torch.randn(rows, E, generator=bench.gen).to(dev)
+    corr = torch.zeros(E, device=dev)
+    ids, wts = torch.empty(rows, top, dtype=torch.int32, device=dev), torch.empty(rows, top, device=dev)
+    rec("moe_route_scored (groups)", timed(lambda: ops.moe_route_scored(logits, corr, top, ids, wts, groups=z["groups"],
+                                                                        scale=2.5)), rows * (E * 4 + top * 8))
+    rec("like: moe_route", timed(lambda: ops.moe_route(logits, top, ids, wts)), rows * (E * 4 + top * 8))
+    ff = z["dense_ff"]
+    h = torch.randn(rows, W, device=dev).to(bf)
+    wgu = torch.randn(2 * ff, W, device=dev).to(bf) * 0.02
+    act = torch.empty(rows, ff, device=dev, dtype=bf)
+    gu_bytes, gu_flops = 2 * ff * W * 2 + rows * (W + ff) * 2, 4 * rows * ff * W
+    rec("gate | up product with gelu in its epilogue", timed(lambda: ops.linear(h, wgu, act, ops.EPI_SWIGLU,
+                                                                                gate_kind=ops.GATE_GELU_TANH)), gu_bytes, gu_flops)
+    rec("like: gate | up product with silu in its epilogue", timed(lambda: ops.linear(h, wgu, act, ops.EPI_SWIGLU)),
+        gu_bytes, gu_flops)
+    rec("like: gate | up product with the clamped form in its epilogue",
+        timed(lambda: ops.linear(h, wgu, act, ops.EPI_SWIGLU, gate=(7.0, 1.702))), gu_bytes, gu_flops)
+    return out
+
+
+def run_bulodra(args) -> int:
+    """Prefill and decode throughput of Bulodra models at layer sizes of real models (random
+    weights) beside the Leguvik models of equal width, depth, vocabulary, attention and experts; and
+    each of its kernels alone beside the like kernels of the other models."""
+    import torch
+    import sonicboom_b200 as sb
+    from sonicboom_b200 import ops
+
+    bench = ArchBench()
+    dev = bench.dev
+    result = {"arch": "bulodra", "impl": "ours", "dtype": "bf16", "peaks": bench.pk, "sizes": {},
+              "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
+              "timing": "CUDA events; kernels alone: median of 5 after 3 warm-up calls, L2 flushed "
+                        "(256 MB written) before each; models: prefill median of 3, decode one region of K steps"}
+    with ClockSampler() as clocks:
+        for name, z in BULODRA_SIZES.items():
+            if args.sizes and name not in args.sizes.split(","):
+                continue
+            lz = dict(width=z["width"], n_layers=z["n_layers"] - 1, vocab=z["vocab"], heads=z["heads"],
+                      kv_heads=z["kv_heads"], dim=z["dim"], window=z["window"], keep_first=64,
+                      s_heads=z["width"] // 32, s_vdim=64, s_state=128, d_heads=z["width"] // 64, d_dim=64,
+                      experts=z["experts"], top=z["top"], expert_ff=z["expert_ff"], shared_ff=z["shared_ff"])
+            rec = {"bulodra_config": {k: list(v) if isinstance(v, tuple) else v for k, v in z.items()}}
+            for label, cfg in (("bulodra", bulodra_config(**z)),
+                               ("leguvik (equal width, vocab, attention heads and window, experts; 7 layers)",
+                                leguvik_config(**lz))):
+                m = sb.random_model(cfg, seed=0, dtype="bfloat16", device=dev, std=0.02)
+                rec[label] = bench.model_points(m, args.prompt, args.batch, args.steps, args.warmup)
+                del m
+                torch.cuda.empty_cache()
+            for rows in (args.prompt, args.batch):
+                rec["kernels_rows_%d" % rows] = bulodra_kernels(bench, z, rows, args.prompt)
+            result["sizes"][name] = rec
+    ops.check_status()
+    result["clocks"] = clocks.summary()
+    print(json.dumps(result))
+    return 0
+
 
 def main() -> int:
     ap = argparse.ArgumentParser()
@@ -1001,14 +1210,15 @@ def main() -> int:
                     help="run one phase only and print a short line (small cases for profilers)")
     ap.add_argument("--eager", action="store_true",
                     help="with --only decode: launch the step kernel by kernel, not as a graph")
-    ap.add_argument("--arch", choices=["qwen2", "zolulix", "mefupel", "leguvik"], default="qwen2",
+    ap.add_argument("--arch", choices=["qwen2", "zolulix", "mefupel", "leguvik", "bulodra"], default="qwen2",
                     help="zolulix: that design's prefill and decode throughput and its kernels alone, "
                          "beside the Qwen2.5 decoder of equal sizes (its own JSON line; the default "
                          "workload is unchanged); mefupel: the same for that design, beside Zolulix and "
                          "Qwen2.5 models of equal sizes; leguvik: the same for that design, beside Mefupel "
-                         "models of equal sizes")
-    ap.add_argument("--sizes", default="", help="with --arch zolulix / mefupel / leguvik: which of its sizes to run (comma separated)")
-    ap.add_argument("--prompt", type=int, default=2048, help="with --arch zolulix / mefupel / leguvik: prompt length")
+                         "models of equal sizes; bulodra: the same for that design, beside Leguvik models of "
+                         "equal sizes")
+    ap.add_argument("--sizes", default="", help="with --arch zolulix / mefupel / leguvik / bulodra: which of its sizes to run (comma separated)")
+    ap.add_argument("--prompt", type=int, default=2048, help="with --arch zolulix / mefupel / leguvik / bulodra: prompt length")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -1023,6 +1233,8 @@ def main() -> int:
         return run_mefupel(args)
     if args.arch == "leguvik":
         return run_leguvik(args)
+    if args.arch == "bulodra":
+        return run_bulodra(args)
     return run(args)
 
 

@@ -33,7 +33,7 @@ CORE = {
     "sb_rope_store": ("i", "piiiiipppppipipiis"),
     "sb_gemm_plain": ("i", _GEMM),
     "sb_gemm_skinny": ("i", _GEMM),
-    "sb_gemm_skinny_gated": ("i", "pipiiiipiffs"),
+    "sb_gemm_skinny_gated": ("i", "pipiiiipiffis"),
     "sb_gemm_tiled": ("i", _GEMM),
     "sb_gemm_tc5": ("i", _GEMM[:-1] + "pziis"),
     "sb_gemm_tc5_ex": ("i", _GEMM[:-1] + "pziips"),

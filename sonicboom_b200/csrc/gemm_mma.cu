@@ -134,9 +134,11 @@ gemm_skinny_kernel(const bf16* X, const bf16* __restrict__ W, int M, int N, int 
       float up = 0.0f;
 #pragma unroll
       for (int w = 0; w < SK_WARPS; ++w) up += partial[w][nt][src_lane][reg + 2];
-      // gate_limit > 0: the clamped form a sigmoid(slope a) (b + 1) instead of silu(gate) * up
+      // gate_limit > 0: the clamped form a sigmoid(slope a) (b + 1) instead of silu(gate) * up;
+      // gate_limit < 0: gelu(gate) * up in gelu's tanh form
       out[(size_t)b * (N / 2) + (m0 / 2 + r)] = sb_from_f32<TO>(
-          gate_limit > 0.0f ? sb_glu_clamped(v, up, gate_limit, gate_slope) : sb_silu(v) * up);
+          gate_limit > 0.0f ? sb_glu_clamped(v, up, gate_limit, gate_slope)
+                            : gate_limit < 0.0f ? sb_gelu_tanh(v) * up : sb_silu(v) * up);
       continue;
     }
     if (n >= N) continue;
@@ -342,14 +344,17 @@ extern "C" int sb_gemm_skinny(const void* A, int a_dtype, const void* W, int w_d
                      1.0f, stream);
 }
 
-// The gated product (SB_EPI_SWIGLU layout) with the clamped activation a sigmoid(slope a) (b + 1),
-// a = min(gate, limit), b = clamp(up, -limit, limit).
+// The gated product (SB_EPI_SWIGLU layout) with the activation `gate_kind` names (SbGate): the clamped
+// form a sigmoid(slope a) (b + 1), a = min(gate, limit), b = clamp(up, -limit, limit), or gelu's tanh form.
 extern "C" int sb_gemm_skinny_gated(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,
                                     int K, void* out, int out_dtype, float gate_limit, float gate_slope,
-                                    cudaStream_t stream) {
-  if (!(gate_limit > 0.0f)) SB_FAIL(SB_ERR_ARG, "sb_gemm_skinny_gated: limit %g must be positive", gate_limit);
+                                    int gate_kind, cudaStream_t stream) {
+  if (gate_kind != SB_GATE_CLAMPED && gate_kind != SB_GATE_GELU_TANH)
+    SB_FAIL(SB_ERR_ARG, "sb_gemm_skinny_gated: gate kind %d", gate_kind);
+  if (gate_kind == SB_GATE_CLAMPED && !(gate_limit > 0.0f))
+    SB_FAIL(SB_ERR_ARG, "sb_gemm_skinny_gated: limit %g must be positive", gate_limit);
   return gemm_skinny(A, a_dtype, W, w_dtype, M, N, K, SB_EPI_SWIGLU, nullptr, 0, nullptr, out, out_dtype,
-                     gate_limit, gate_slope, stream);
+                     gate_kind == SB_GATE_GELU_TANH ? -1.0f : gate_limit, gate_slope, stream);
 }
 
 extern "C" int sb_gemm_tiled(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,

@@ -66,10 +66,25 @@ __device__ __forceinline__ float sb_silu_out(float x) {
   return sb_silu(x);
 }
 
+// gelu in its tanh form of a value that is rounded to TO afterwards: 0.5 z (1 + tanh(y)) =
+// z (1 - 1 / (exp(2y) + 1)), y = sqrt(2/pi) (z + 0.044715 z^3); for bfloat16 outputs with the
+// hardware's exponential and reciprocal (an exponential that overflows gives z, one that
+// underflows 0, as they should), for float32 outputs the accurate tanhf.
+template <typename TO>
+__device__ __forceinline__ float sb_gelu_out(float z) {
+  if (sizeof(TO) == 2) {
+    const float y2 = 1.5957691216057308f * (z + 0.044715f * z * z * z);
+    return z * (1.0f - __frcp_rn(__expf(y2) + 1.0f));
+  }
+  return sb_gelu_tanh(z);
+}
+
 // What the gated epilogue makes of a gate and its up value: silu(gate) * up, or, with a limit,
-// a sigmoid(slope a) (b + 1) with a = min(gate, limit), b = clamp(up, -limit, limit).
+// a sigmoid(slope a) (b + 1) with a = min(gate, limit), b = clamp(up, -limit, limit), or
+// gelu(gate) * up when the kind says so.
 template <typename TO, typename P>
 __device__ __forceinline__ float sb_gated(const P& p, float gate, float up) {
+  if (p.gate_kind == SB_GATE_GELU_TANH) return sb_gelu_out<TO>(gate) * up;
   if (p.gate_limit > 0.0f) return sb_glu_clamped(gate, up, p.gate_limit, p.gate_slope);
   return sb_silu_out<TO>(gate) * up;
 }
@@ -92,6 +107,7 @@ struct Tc5Params {
   size_t warm_bytes;
   int rowwise;                 // the many-rows epilogue may use 16-byte accesses along a row
   float gate_limit, gate_slope;   // gated epilogue: limit > 0 selects the clamped form, else silu(gate) * up
+  int gate_kind;                  // SB_GATE_GELU_TANH: gelu(gate) * up; else by gate_limit
 };
 
 constexpr int stage_bytes(int bn) { return (BM + bn) * BK * 2; }
@@ -596,7 +612,9 @@ tc5_reduce_kernel(const Tc5Params p, int bn) {
     const int o = o0 + i;
     if (o >= n_out) break;
     float v = acc[i];
-    if (p.epilogue == SB_EPI_SWIGLU) v = p.gate_limit > 0.0f ? sb_glu_clamped(v, up[i], p.gate_limit, p.gate_slope) : sb_silu(v) * up[i];
+    if (p.epilogue == SB_EPI_SWIGLU)
+      v = p.gate_kind == SB_GATE_GELU_TANH ? sb_gelu_tanh(v) * up[i]
+          : p.gate_limit > 0.0f ? sb_glu_clamped(v, up[i], p.gate_limit, p.gate_slope) : sb_silu(v) * up[i];
     else if (p.epilogue == SB_EPI_BIAS)
       v += p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, o) : bias_at<bf16>(p.bias, o);
     else if (p.epilogue == SB_EPI_RESIDUAL) v += p.residual[(size_t)j * p.N + o];
@@ -1127,6 +1145,7 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
   p.rowwise = rowwise_on && N % 16 == 0 && (((uintptr_t)out | (uintptr_t)residual | (uintptr_t)bias) & 15) == 0;
   p.gate_limit = extras && epilogue == SB_EPI_SWIGLU ? extras->gate_limit : 0.0f;
   p.gate_slope = extras ? extras->gate_slope : 1.0f;
+  p.gate_kind = extras && epilogue == SB_EPI_SWIGLU ? extras->gate_kind : SB_GATE_SILU;
   p.warm = extras ? (const char*)extras->warm : nullptr;
   p.warm_bytes = extras ? sb_warm_bytes(extras->warm, extras->warm_bytes) : 0;
   CUtensorMap ma, mb;

@@ -77,6 +77,7 @@ typedef struct SbLinearExtras {
   const SbRopeStore* rope;     /* null: none; only where sb_gemm_tc5_fuses_rope says so */
   float gate_limit;            /* SB_EPI_SWIGLU only: > 0 makes the gated epilogue a sigmoid(gate_slope a) (b + 1), */
   float gate_slope;            /* a = min(gate, limit), b = clamp(up, -limit, limit); 0: silu(gate) * up */
+  int gate_kind;               /* SB_EPI_SWIGLU only: SB_GATE_GELU_TANH makes it gelu(gate) * up; else by gate_limit */
 } SbLinearExtras;
 
 /* One row's sampling record (sb_sample reads an array of them from device memory). */
@@ -122,9 +123,10 @@ int sb_gemm_plain(const void* A, int a_dtype, const void* W, int w_dtype, int M,
 int sb_gemm_skinny(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N, int K,
                    int epilogue, const void* bias, int bias_dtype, const float* residual,
                    void* out, int out_dtype, sb_stream_t stream);
-/* sb_gemm_skinny with SB_EPI_SWIGLU's layout and the clamped gated activation (see SbLinearExtras). */
+/* sb_gemm_skinny with SB_EPI_SWIGLU's layout and the gated activation gate_kind names (SB_GATE_CLAMPED
+ * with its limit and slope, or SB_GATE_GELU_TANH; see SbLinearExtras). */
 int sb_gemm_skinny_gated(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N, int K,
-                         void* out, int out_dtype, float gate_limit, float gate_slope,
+                         void* out, int out_dtype, float gate_limit, float gate_slope, int gate_kind,
                          sb_stream_t stream);
 int sb_gemm_tiled(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N, int K,
                   int epilogue, const void* bias, int bias_dtype, const float* residual,

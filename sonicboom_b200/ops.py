@@ -186,8 +186,9 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
     tcgen05 and the weight-streaming kernels where they run, else as the plain product followed
     by `glu_clamped`.
 
-    `gate_kind` = GATE_GELU_TANH with EPI_SWIGLU: gelu(gate) * up in gelu's tanh form, as the plain
-    product followed by `gated_act`.
+    `gate_kind` = GATE_GELU_TANH with EPI_SWIGLU: gelu(gate) * up in gelu's tanh form, in the same
+    places (inside the tcgen05 and the weight-streaming kernels, else the plain product followed by
+    `gated_act`).
 
     `norm` = (weight, eps, norm_out) also writes norm_out = rmsnorm(out, weight, eps) [M,N]
     (out must be float32): in the kernel that finishes the product where one does (the split-K
@@ -213,23 +214,22 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
         if w.dtype != torch.float32:
             raise KernelError("linear: a float32 activation needs float32 weights")
     if gate_kind == GATE_GELU_TANH:
-        assert epilogue == EPI_SWIGLU and N % (2 * SWIGLU_BLOCK) == 0 and gate is None
-        gu = torch.empty((M, N), dtype=torch.float32, device=a.device)
-        linear(a, w, gu, EPI_NONE, kernel=kernel)
-        return gated_act(gu, GATE_GELU_TANH, out, interleaved=True)
-    if gate is not None:
+        assert epilogue == EPI_SWIGLU and gate is None
+    if gate is not None or gate_kind == GATE_GELU_TANH:
         assert epilogue == EPI_SWIGLU and N % (2 * SWIGLU_BLOCK) == 0
+        limit, slope = gate if gate is not None else (0.0, 1.0)
+        kind = GATE_CLAMPED if gate is not None else GATE_GELU_TANH
         picked = kernel if kernel != "auto" else _pick_kernel(M, N, K, a.device)
         fused = a.dtype == torch.bfloat16 and K % 8 == 0 and picked == "tc5"
         if a.dtype == torch.bfloat16 and K % 8 == 0 and picked == "skinny" and M <= SKINNY_MAX_ROWS:
             _check(lib().sb_gemm_skinny_gated(_ptr(a), BF16, _ptr(w), BF16, M, N, K, _ptr(out), _code(out.dtype),
-                                              ctypes.c_float(gate[0]), ctypes.c_float(gate[1]), _stream()),
+                                              ctypes.c_float(limit), ctypes.c_float(slope), kind, _stream()),
                    "linear (weight-streaming kernel, gated)")
             return out
         if not fused:
             gu = torch.empty((M, N), dtype=torch.float32, device=a.device)
             linear(a, w, gu, EPI_NONE, kernel=kernel)
-            return glu_clamped(gu, gate[0], gate[1], out, interleaved=True)
+            return gated_act(gu, kind, out, interleaved=True, limit=limit, slope=slope)
         kernel = "tc5"
     args = (_ptr(a), _code(a.dtype), _ptr(w), _code(w.dtype), M, N, K, epilogue, _ptr(bias),
             _code(bias.dtype) if bias is not None else 0, _ptr(residual), _ptr(out),
@@ -258,8 +258,9 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
         form = 1 if kernel == "tc5_normal" else 0
         ws = _tc5_workspace(M, N, K, a.device) if form == 0 else None
         extras = None
-        if norm is not None or (warm is not None and WARM) or gate is not None:
+        if norm is not None or (warm is not None and WARM) or gate is not None or gate_kind == GATE_GELU_TANH:
             extras = LinearExtras()
+            extras.gate_kind = gate_kind if gate_kind == GATE_GELU_TANH else 0
             if gate is not None:
                 extras.gate_limit, extras.gate_slope = float(gate[0]), float(gate[1])
             if norm is not None:
@@ -298,7 +299,7 @@ class LinearExtras(ctypes.Structure):
                 ("norm_eps", ctypes.c_float), ("norm_out", ctypes.c_void_p),
                 ("norm_out_dtype", ctypes.c_int), ("warm", ctypes.c_void_p),
                 ("warm_bytes", ctypes.c_size_t), ("rope", ctypes.POINTER(RopeStore)),
-                ("gate_limit", ctypes.c_float), ("gate_slope", ctypes.c_float)]
+                ("gate_limit", ctypes.c_float), ("gate_slope", ctypes.c_float), ("gate_kind", ctypes.c_int)]
 
 
 def qkv_rope_store(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, n_q_heads: int,

@@ -66,21 +66,28 @@ struct AttnParams {
   int n_q_heads, n_kv_heads, window, n_splits;
   int n_seqs;
   float scale_log2;            // scale * log2(e)
-  float cap_a, cap_b;          // a score cap c > 0: cap_a = 2 scale / c, cap_b = c log2(e); else both 0
+  float cap_a, cap_b;          // a score cap c > 0: cap_a = scale / c, cap_b = c log2(e); else both 0
   const float* sink;           // [n_q_heads] or null: exp(sink) joins each row's softmax denominator
   const char* warm;            // decode: bytes the next kernel will read, asked into L2 (or null)
   size_t warm_bytes;
 };
 
 // A raw dot product to the exponent's argument: score * log2(e) with score = dot * scale, or, with
-// a cap c, score = c tanh(dot * scale / c) written as c (1 - 2 / (exp(2 dot scale / c) + 1)).
-// Monotone in the dot product, so the largest dot product gives the largest result.
+// a cap c, score = c tanh(dot * scale / c).  The hyperbolic tangent is the hardware's
+// (tanh.approx.f32, relative error 2^-11: at most a few thousandths of the capped score, the size
+// of the bfloat16 rounding of the weights it ends in), one special-function instruction where
+// exponential and division would be two, which is what the softmax threads of the tensor-memory
+// kernel are bound by.  Monotone in the dot product, so the largest dot product gives the largest result.
 struct ScoreMap {
   float scale_log2, cap_a, cap_b;
 };
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float mapped_score(float dot, const ScoreMap& sm) {
-  return sm.cap_b != 0.0f ? sm.cap_b * (1.0f - __fdividef(2.0f, __expf(dot * sm.cap_a) + 1.0f))
-                          : dot * sm.scale_log2;
+  return sm.cap_b != 0.0f ? sm.cap_b * tanh_approx(dot * sm.cap_a) : dot * sm.scale_log2;
 }
 __device__ __forceinline__ ScoreMap score_map(const AttnParams& p) {
   return ScoreMap{p.scale_log2, p.cap_a, p.cap_b};
@@ -700,7 +707,7 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.n_seqs = n_seqs;
   p.scale_log2 = scale * LOG2E;
   if (softcap < 0.0f) SB_FAIL(SB_ERR_ARG, "sb_attention: score cap %g (0: none)", softcap);
-  p.cap_a = softcap > 0.0f ? 2.0f * scale / softcap : 0.0f;
+  p.cap_a = softcap > 0.0f ? scale / softcap : 0.0f;
   p.cap_b = softcap > 0.0f ? softcap * LOG2E : 0.0f;
   const int G = n_q_heads / n_kv_heads;
   static bool configured = false;

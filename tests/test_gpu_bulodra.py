@@ -254,6 +254,7 @@ ONE_LAYER = {
     "attention, plain rotation of the whole head": layer("attention", attention(2, 1, 32, 32, rot(100.0, 32))),
     "latent attention": layer("latent_attention", latent(3, 16, 8, 12, 24, 20, rot(5000.0, 8, (4.0, 32, 8.0, 1.0)))),
     "latent attention, few turned dimensions": layer("latent_attention", latent(2, 8, 16, 16, 16, 40, rot(300.0, 6))),
+    "latent attention, more heads than one decode call takes": layer("latent_attention", latent(20, 8, 8, 8, 24, 16, rot(1000.0, 8))),
     "capped attention in a window": layer("attention_2", attention_2(4, 2, 16, 8, rot(10000.0, 8), 9, 5.0, scale=0.6)),
     "capped attention, no window": layer("attention_2", attention_2(2, 2, 16, 16, rot(10000.0, 16), 0, 3.0, scale=0.9)),
     "dense feed-forward": layer("attention_2", attention_2(1, 1, 16, 16, rot(10.0, 4), 2, 9.0), dense(56)),

@@ -988,23 +988,23 @@ def bulodra_config(width, n_layers, vocab, heads, kv_heads, dim, window, l_dim, 
     """A Bulodra model of the given layer sizes: attention over a latent, two capped attentions in a
     window, one attention with a sink, and so on in turn; the first layer with a dense feed-forward,
     the others with a mixture of experts in groups and a shared expert."""
-    yarn = {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+    yarn = {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}
     kinds = [("latent_attention", {"heads": heads, "dim": l_dim, "rot_dim": l_rot, "vdim": l_vdim, "kv_rank": kv_rank,
                                    "q_rank": q_rank, "scale": (l_dim + l_rot) ** -0.5,
-                                   "rot": {"base": 1e6, "dims": l_rot, "scaling": yarn}}),
+                                   "rot": {"base": 1e5, "dims": l_rot, "scaling": yarn}}),
              ("attention_2", {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
-                              "softcap": 30.0, "mask": {"size": window}, "rot": {"base": 5e5, "dims": dim // 2}}),
+                              "softcap": 50.0, "mask": {"size": window}, "rot": {"base": 1e4, "dims": dim // 2}}),
              ("attention_2", {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
-                              "softcap": 30.0, "mask": {"size": window}, "rot": {"base": 5e5, "dims": dim // 2}}),
+                              "softcap": 50.0, "mask": {"size": window}, "rot": {"base": 1e4, "dims": dim // 2}}),
              ("attention", {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
-                            "rot": {"base": 5e5, "dims": dim, "scaling": yarn}})]
-    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.5,
+                            "rot": {"base": 1e4, "dims": dim, "scaling": yarn}})]
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.0,
                                      "groups": {"count": groups[0], "keep": groups[1]}},
            "expert": {"ff": expert_ff, "limit": 7.0}, "shared": {"ff": shared_ff, "limit": 7.0}}
     layers = [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1],
                "mlp": {"kind": "dense", "ff": dense_ff} if i == 0 else moe} for i in range(n_layers)]
-    return {"architecture": "Bulodra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
-            "logit_scale": 0.25, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 36313, "mul_cur": 27191}},
+    return {"architecture": "Bulodra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.6,
+            "logit_scale": 0.5, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 36313, "mul_cur": 27191}},
             "layers": layers}
 
 
@@ -1072,7 +1072,7 @@ def bulodra_kernels(bench, z, rows, context):
     n_in = (H + 2 * G) * d + H
     proj = torch.randn(rows, n_in, device=dev)
     q = torch.empty(rows, H, d, device=dev, dtype=bf)
-    table = frequency_table(5e5, d, dev)
+    table = frequency_table(1e4, d, dev)
     hw, kw = torch.ones(d, device=dev, dtype=bf), torch.ones(d, device=dev, dtype=bf)
     prep_bytes = rows * ((H + 2 * G) * d * 4 + (H + 2 * G) * d * 2)
 
@@ -1096,7 +1096,7 @@ def bulodra_kernels(bench, z, rows, context):
     att_bytes, att_flops = kv_bytes + rows * H * d * 4, 4 * keys * H * d
     grp0 = cache.group_of_entry[0]
     rec(f"attention, capped scores ({kind}; window {win})",
-        timed(lambda: ops.attention(q, o, plan, grp0, store0, H, G, d, win, d ** -0.5, softcap=30.0)), att_bytes, att_flops)
+        timed(lambda: ops.attention(q, o, plan, grp0, store0, H, G, d, win, d ** -0.5, softcap=50.0)), att_bytes, att_flops)
     rec(f"like: attention ({kind}; window {win})",
         timed(lambda: ops.attention(q, o, plan, grp0, store0, H, G, d, win, d ** -0.5)), att_bytes, att_flops)
     sink = torch.zeros(H, device=dev)
@@ -1120,7 +1120,7 @@ def bulodra_kernels(bench, z, rows, context):
     lproj = torch.randn(rows, H * (ld + lr), device=dev)
     qwide = torch.empty(1, rows, H, wide, device=dev, dtype=bf)
     cn = torch.ones(rank, device=dev, dtype=bf)
-    ltab = frequency_table(1e6, lr, dev)
+    ltab = frequency_table(1e5, lr, dev)
     lbytes = rows * (H * lr * 6 + wide * 4 + wide * 4)
     rec("latent_prep, pairs half the part apart, the latent in rows of its own",
         timed(lambda: ops.latent_prep(lproj, H, ld, lr, rank, lr, ltab, plan.row_seq, plan.row_pos, g1.page_off, g1.page_ids,
@@ -1136,7 +1136,7 @@ def bulodra_kernels(bench, z, rows, context):
     corr = torch.zeros(E, device=dev)
     ids, wts = torch.empty(rows, top, dtype=torch.int32, device=dev), torch.empty(rows, top, device=dev)
     rec("moe_route_scored (groups)", timed(lambda: ops.moe_route_scored(logits, corr, top, ids, wts, groups=z["groups"],
-                                                                        scale=2.5)), rows * (E * 4 + top * 8))
+                                                                        scale=2.0)), rows * (E * 4 + top * 8))
     rec("like: moe_route", timed(lambda: ops.moe_route(logits, top, ids, wts)), rows * (E * 4 + top * 8))
     ff = z["dense_ff"]
     h = torch.randn(rows, W, device=dev).to(bf)

@@ -84,8 +84,8 @@ CONFIGS = {
     "B": model(150, 44, [
         layer("attention", attention(6, 3, 64, 32, rot(100000.0, 32, (8.0, 64, 4.0, 0.5)), scale=0.1),
               moe(8, 3, 10, 1.0, groups=(4, 3), scale=0.8, shared=(18, 2.0))),
-        layer("attention_2", attention_2(2, 1, 64, 64, rot(500000.0, 16), window=70, softcap=30.0, scale=0.11),
-              moe(4, 2, 9, 1.2, groups=(2, 1), scale=2.5)),
+        layer("attention_2", attention_2(2, 1, 64, 64, rot(200000.0, 24), window=70, softcap=20.0, scale=0.11),
+              moe(4, 2, 9, 1.2, groups=(2, 1), scale=2.2)),
         layer("latent_attention", latent(2, 24, 16, 20, 48, 12, rot(10000.0, 16, (2.0, 128, 16.0, 2.0))), dense(16)),
         layer("attention_2", attention_2(3, 3, 8, 8, rot(50.0, 2), window=3, softcap=1.5, scale=0.5), moe(3, 2, 16, 0.7)),
     ], bigram=(53, 11, 3), mult=1.0, logit_scale=1.0, eps=1e-6),

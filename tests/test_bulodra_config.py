@@ -81,8 +81,8 @@ def test_errors_name_the_key(edit, key):
     assert key in str(e.value)
 
 
-@pytest.mark.parametrize("base,n,scaling", [(10000.0, 8, (4.0, 32, 8.0, 1.0)), (500000.0, 64, (8.0, 512, 32.0, 1.0)),
-                                            (1e6, 32, (2.0, 2048, 32.0, 1.0)), (50.0, 2, (16.0, 8, 1.0, 0.25)),
+@pytest.mark.parametrize("base,n,scaling", [(10000.0, 8, (4.0, 32, 8.0, 1.0)), (300000.0, 64, (6.0, 256, 16.0, 2.0)),
+                                            (2e6, 48, (3.0, 1024, 24.0, 1.5)), (50.0, 2, (16.0, 8, 1.0, 0.25)),
                                             (20000.0, 16, (3.0, 48, 6.0, 0.5))])
 def test_stretched_rotation_frequencies(base, n, scaling):
     f, mag = yarn_frequencies(base, n, *scaling)

@@ -117,7 +117,7 @@ def test_gelu_gate_and_scale_and_norm_of_a_row_prefix():
     assert rel_err(out, pb.rms(wide[:, :20].double(), 1e-5) * w.double()) < 2e-6
 
 
-@pytest.mark.parametrize("experts,top,groups,scale", [(6, 2, (3, 2), 1.7), (8, 3, (4, 3), 0.8), (4, 2, (2, 1), 2.5),
+@pytest.mark.parametrize("experts,top,groups,scale", [(6, 2, (3, 2), 1.7), (8, 3, (4, 3), 0.8), (4, 2, (2, 1), 2.2),
                                                       (5, 1, None, 1.0), (64, 6, (8, 4), 2.0), (6, 3, (6, 4), 1.0),
                                                       (12, 12, (3, 3), 1.0), (40, 4, (1, 1), 1.0)])
 def test_router_scores_groups_and_weights(experts, top, groups, scale):
@@ -217,10 +217,10 @@ ATTEND = [
     # hq, hkv, dim, vdim, window, rotation, head_norm, sink, softcap, gate
     (4, 2, 16, 24, 9, rot(10000.0, 8), "after", False, 5.0, True),
     (6, 3, 64, 32, 0, rot(100000.0, 32, (8.0, 64, 4.0, 0.5)), "before", True, 0.0, False),
-    (2, 1, 64, 64, 70, rot(500000.0, 16), "after", False, 30.0, True),
-    (8, 2, 128, 128, 100, rot(500000.0, 64), "after", False, 20.0, True),
+    (2, 1, 64, 64, 70, rot(200000.0, 24), "after", False, 20.0, True),
+    (8, 2, 128, 128, 100, rot(70000.0, 64), "after", False, 12.0, True),
     (3, 3, 8, 8, 3, rot(50.0, 2), "after", False, 1.5, False),
-    (4, 1, 96, 96, 0, rot(500000.0, 96, (8.0, 512, 32.0, 1.0)), "before", True, 0.0, False),
+    (4, 1, 96, 96, 0, rot(300000.0, 64, (6.0, 256, 16.0, 2.0)), "before", True, 0.0, False),
     (2, 2, 48, 40, 33, rot(1000.0, 0), None, True, 4.0, True),
 ]
 
@@ -350,7 +350,7 @@ def sharp_model():
     return model(80, 48, [
         layer("attention_2", attention_2(2, 1, 16, 16, rot(10000.0, 8), window=13, softcap=40.0, scale=1.2)),
         layer("attention", attention(2, 2, 16, 16, rot(10000.0, 16, (4.0, 64, 8.0, 1.0)), scale=0.7), dense(32)),
-        layer("attention_2", attention_2(2, 2, 32, 32, rot(500000.0, 16), window=70, softcap=25.0, scale=0.5)),
+        layer("attention_2", attention_2(2, 2, 32, 32, rot(40000.0, 16), window=70, softcap=25.0, scale=0.5)),
         layer("latent_attention", latent(2, 16, 8, 16, 24, 16, rot(10000.0, 8), scale=0.5)),
     ], mult=1.0, logit_scale=1.0)
 

@@ -127,7 +127,8 @@ _CALM = {}
 
 def calm_tokens(cfg, tensors, n, seed, key=None, margin=ROUTER_MARGIN):
     """`n` seeded random tokens at none of which a router's choice is a close call (the last chosen
-    expert's choice score is at least `margin` above the best one left out), so that rounding cannot
+    expert's choice score is at least `margin` above the best one left out, and the last kept group's
+    score at least `margin` above the best group left out), so that rounding cannot
     send a token to other experts than the plain implementation does.  A position's routing depends on
     the tokens up to it only: the first close call's token is drawn again until none is left.  Returns
     (tokens, the plain implementation's logits)."""

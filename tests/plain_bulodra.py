@@ -167,24 +167,30 @@ def expert(h, get, limit):
 
 
 def route(z, correction, r):
-    """z [experts] router logits of one token -> (chosen experts, their weights).  Close calls
-    (gap between the last chosen and the first not chosen) are the caller's to look at."""
+    """z [experts] router logits of one token -> (chosen experts, their weights, margin).  The margin
+    is how far the choice is from falling another way: the last chosen expert's choice score above
+    the best one left out, and the last kept group's score above the best group left out."""
     E, top = r["experts"], r["top"]
     s = torch.sigmoid(z)
     choice = s + correction
     groups = r.get("groups")
     allowed = list(range(E))
+    gap = math.inf
     if groups is not None:
         n, per = groups["count"], E // groups["count"]
         score = []
         for gi in range(n):
             part = sorted((float(x) for x in choice[gi * per:(gi + 1) * per]), reverse=True)
             score.append(sum(part[:2]))
-        best = sorted(range(n), key=lambda gi: (-score[gi], gi))[:groups["keep"]]
+        ranked = sorted(range(n), key=lambda gi: (-score[gi], gi))
+        best = ranked[:groups["keep"]]
+        if len(ranked) > groups["keep"]:
+            gap = score[ranked[groups["keep"] - 1]] - score[ranked[groups["keep"]]]
         allowed = [e for e in range(E) if e // per in best]
     order = sorted(allowed, key=lambda e: (-float(choice[e]), e))
     chosen = order[:top]
-    gap = float(choice[order[top - 1]] - choice[order[top]]) if len(order) > top else math.inf
+    if len(order) > top:
+        gap = min(gap, float(choice[order[top - 1]] - choice[order[top]]))
     return chosen, [float(s[e]) * r["scale"] for e in chosen], gap
 
 
